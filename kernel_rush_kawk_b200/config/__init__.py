@@ -4,6 +4,7 @@ from .base import ConfigError, ModelConfig
 from .qwen3 import Qwen3Config
 from .taredra import TaredraConfig
 from .disorax import DisoraxConfig
+from .zadunex import ZadunexConfig
 from .registry import (Architecture, architecture_name, get_architecture, known_architectures, preset_config,
                        read_config, register_architecture)
 

@@ -88,7 +88,8 @@ class Engine:
         self.ops = ops if ops is not None else _default_ops(self.device, head_dims)
         expected = tree.expected_tensors()
         if _tensors is None:
-            tensors = read_checkpoint(self.model_path, expected, self.device, self.dtype, self.plan.duplicates)
+            tensors = read_checkpoint(self.model_path, expected, self.device, self.dtype, self.plan.duplicates,
+                                      self.plan.ignored)
         else:
             tensors = {}
             for name, spec in expected.items():

@@ -17,5 +17,7 @@ from .sink_attention import SinkWindowAttention
 from .recurrent import DeltaRule, TimeMixWKV
 from .latent_attention import LatentAttention
 from .moe import RoutedExperts
+from .hyper import HyperRMSNorm
+from .ssm import Mamba2
 
 __all__ = [n for n in dir() if not n.startswith("_")]

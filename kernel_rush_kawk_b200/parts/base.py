@@ -160,15 +160,19 @@ class Stream:
 
     A layer whose mixer and feed-forward read the same x leaves two pending outputs
     (``branch`` and ``branch2``) and a multiplier for their sum (``scale``):
-    the next norm computes x + scale * (branch + branch2)."""
+    the next norm computes x + scale * (branch + branch2).
 
-    __slots__ = ("x", "branch", "branch2", "scale")
+    With hyper-connections ``x`` holds several streams side by side and ``fold`` the
+    weights with which the pending output is written back into them (parts/hyper.py)."""
 
-    def __init__(self, x, branch=None, branch2=None, scale=1.0):
+    __slots__ = ("x", "branch", "branch2", "scale", "fold")
+
+    def __init__(self, x, branch=None, branch2=None, scale=1.0, fold=None):
         self.x = x
         self.branch = branch
         self.branch2 = branch2
         self.scale = scale
+        self.fold = fold
 
 
 # ----------------------------------------------------------------------------

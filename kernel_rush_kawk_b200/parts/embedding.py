@@ -30,13 +30,14 @@ class TokenEmbedding(Embedding):
 
 
 class OutputHead(Head):
-    """params: vocab, hidden. The plan points "weight" at the embedding table's
-    checkpoint name when the head is tied."""
+    """params: vocab, hidden, scale (default 1: the logits are multiplied by it). The plan points
+    "weight" at the embedding table's checkpoint name when the head is tied."""
 
     def __init__(self, params):
         super().__init__(params)
         self.vocab = int(params["vocab"])
         self.hidden = int(params["hidden"])
+        self.scale = float(params.get("scale", 1.0))
         self.weight = None
 
     def tensor_specs(self):
@@ -47,7 +48,8 @@ class OutputHead(Head):
 
     def forward(self, ctx, h):
         """h: normalised rows (a Normed or a tensor) of the wanted positions."""
-        return ctx.ops.linear(h, self.weight, out_float32=True)
+        logits = ctx.ops.linear(h, self.weight, out_float32=True)
+        return logits if self.scale == 1.0 else logits.mul_(self.scale)
 
 
 register_embedding("token_embedding", TokenEmbedding)

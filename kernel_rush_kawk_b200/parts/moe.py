@@ -26,7 +26,9 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 class RoutedExperts(FeedForward):
     """params: hidden, experts, top, intermediate, activation ("silu"), shared_intermediate (None or int),
-    shared_gate (bool: the shared expert sits behind sigmoid(Wsg h))."""
+    shared_gate (bool: the shared expert sits behind sigmoid(Wsg h)), router_bias (default True: the router
+    has a bias "router.b"), weights ("chosen", the default: softmax over the chosen logits; "all": each chosen
+    expert's share of the softmax over all experts, not renormalised)."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -38,6 +40,10 @@ class RoutedExperts(FeedForward):
         self.activation = str(p.get("activation", "silu"))
         self.shared = None if p.get("shared_intermediate") is None else int(p["shared_intermediate"])
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared is not None
+        self.router_bias = bool(p.get("router_bias", True))
+        self.weights = str(p.get("weights", "chosen"))
+        if self.weights not in ("chosen", "all"):
+            raise ValueError(f"weights must be 'chosen' or 'all', got {self.weights!r}")
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"a token takes between 1 and {self.experts} experts, got top = {self.top}")
         if self.top > 32:
@@ -45,7 +51,9 @@ class RoutedExperts(FeedForward):
 
     def tensor_specs(self):
         H, F = self.hidden, self.intermediate
-        specs = {"router": TensorSpec((self.experts, H)), "router.b": TensorSpec((self.experts,), "vector")}
+        specs = {"router": TensorSpec((self.experts, H))}
+        if self.router_bias:
+            specs["router.b"] = TensorSpec((self.experts,), "vector")
         for e in range(self.experts):
             specs[f"e{e}.gate"] = TensorSpec((F, H))
             specs[f"e{e}.up"] = TensorSpec((F, H))
@@ -62,7 +70,7 @@ class RoutedExperts(FeedForward):
         E = self.experts
         # in the path's dtype: the logits' product accumulates in 32-bit; the shared expert's gate is its last row
         self.router_w = torch.cat([tensors["router"]] + ([tensors["shared.sg"]] if self.shared_gate else []), dim=0).contiguous()
-        self.router_b = tensors["router.b"].float().contiguous()
+        self.router_b = tensors["router.b"].float().contiguous() if self.router_bias else None
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0) for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         self.w_shared_in = self.w_shared_down = None
@@ -76,7 +84,11 @@ class RoutedExperts(FeedForward):
         base = None
         if self.shared is not None:
             base = ops.linear(ops.gate_up_act(x, self.w_shared_in, self.shared, self.activation), self.w_shared_down)
-        experts, weights, row_gate = ops.moe_route(x, self.router_w, self.router_b, self.top, gate_row=self.shared_gate)
+        if self.weights == "all":
+            experts, weights, row_gate = ops.moe_route(x, self.router_w, self.router_b, self.top, gate_row=self.shared_gate,
+                                                       over_all=True)
+        else:
+            experts, weights, row_gate = ops.moe_route(x, self.router_w, self.router_b, self.top, gate_row=self.shared_gate)
         return ops.moe_experts(x, self.w_gate_up, self.w_down, experts, weights, self.intermediate, self.activation,
                                add=base, add_gate=row_gate, batch=ctx.batch)
 

@@ -80,8 +80,11 @@ class ModelPlan:
     #: checkpoint names that may be present although no part asks for them, if they
     #: equal the named other tensor (a tied head stored twice): name -> same-as name
     duplicates: Mapping = field(default_factory=dict)
+    #: checkpoint names that may be present and are not read (the norm of a feed-forward that a layer lacks)
+    ignored: tuple[str, ...] = ()
 
     def __post_init__(self):
+        object.__setattr__(self, "ignored", tuple(self.ignored))
         object.__setattr__(self, "layers", tuple(self.layers))
         object.__setattr__(self, "schedule", tuple(self.schedule))
         object.__setattr__(self, "duplicates", _frozen(self.duplicates))

@@ -18,6 +18,12 @@ element ("element"); Wg h rides in the stacked input product. ``value_mix``: val
 are blended across layers of one step: the layer marked "first" leaves its values of
 the step's tokens under ``value_mix_key``, a layer marked "blend" caches
 (1 - lambda) v + lambda v_first with its own scalar lambda (tensor "vmix").
+
+Three options of the projections and the sink. ``bias``: q, k and v have biases (tensors "q.b", "k.b", "v.b").
+``qk_norm`` "row": the whole q row (all heads together) is divided by its root mean square and multiplied
+by a weight of the row's size ("q.norm"), and the k row likewise ("k.norm"), after the biases and before the
+rotation, in 32-bit. ``sink`` "zero": the extra term of the softmax's denominator is exp(0) for every head,
+p_j = exp(s_j) / (1 + sum exp(s_j)), and no tensor is read for it.
 """
 
 from __future__ import annotations
@@ -31,7 +37,8 @@ from .branches import Branch
 class SinkWindowAttention(Branch):
     """params: hidden, heads, kv_heads, dim, vdim, scale, window (None or int), rot_dims, rot_base,
     value_norm (bool), sink (bool), eps, keep_first (int), gate (None, "head" or "element"),
-    value_mix (None, "first" or "blend"), value_mix_key."""
+    value_mix (None, "first" or "blend"), value_mix_key, bias (bool), qk_norm (None or "row"); sink may
+    be "zero"."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -46,7 +53,12 @@ class SinkWindowAttention(Branch):
         self.rot_dims = int(p.get("rot_dims", 0))
         self.rot_base = float(p.get("rot_base", 10000.0))
         self.value_norm = bool(p.get("value_norm", False))
-        self.has_sink = bool(p.get("sink", False))
+        self.zero_sink = p.get("sink") == "zero"
+        self.has_sink = bool(p.get("sink", False)) and not self.zero_sink
+        self.bias = bool(p.get("bias", False))
+        self.qk_norm = p.get("qk_norm")
+        if self.qk_norm not in (None, "row"):
+            raise ValueError(f"qk_norm must be None or 'row', got {self.qk_norm!r}")
         self.eps = float(p.get("eps", 0.0))
         self.keep_first = int(p.get("keep_first") or 0) if self.window is not None else 0
         self.gate = p.get("gate")
@@ -70,6 +82,13 @@ class SinkWindowAttention(Branch):
             specs["sink"] = TensorSpec((self.heads,), "vector")
         if self.gate:
             specs["g"] = TensorSpec((self.heads * (self.vdim if self.gate == "element" else 1), self.hidden))
+        if self.bias:
+            specs.update({"q.b": TensorSpec((self.heads * self.dim,), "vector"),
+                          "k.b": TensorSpec((self.kv_heads * self.dim,), "vector"),
+                          "v.b": TensorSpec((self.kv_heads * self.vdim,), "vector")})
+        if self.qk_norm:
+            specs.update({"q.norm": TensorSpec((self.heads * self.dim,), "gain"),
+                          "k.norm": TensorSpec((self.kv_heads * self.dim,), "gain")})
         if self.value_mix:
             specs["vmix"] = TensorSpec((), "vector")  # the first layer of a blend stores one too and never reads it
         return specs
@@ -91,6 +110,11 @@ class SinkWindowAttention(Branch):
         self.w = {k: tensors[k] for k in ("q", "k", "v", "o") + (("g",) if self.gate else ())}
         self.lam = float(tensors["vmix"].float().item()) if self.value_mix == "blend" else None
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
+        if self.zero_sink:
+            self.sink = torch.zeros(self.heads, dtype=torch.float32, device=runtime.device)
+        f = lambda *keys: torch.cat([tensors[k].float().reshape(-1) for k in keys]).contiguous()
+        self.qkv_bias = f("q.b", "k.b", "v.b") if self.bias else None
+        self.qk_gain = f("q.norm", "k.norm") if self.qk_norm else None
         # the few rotation frequencies come from the host in 64-bit, so that they depend on no device's pow()
         # and as two floats each (the float32 value, then what float32 leaves of the float64 value)
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
@@ -110,6 +134,9 @@ class SinkWindowAttention(Branch):
         k_col = self.heads * self.dim
         v_col = k_col + self.kv_heads * self.dim
         value_eps = self.eps if self.value_norm else None
+        if self.bias or self.qk_norm:  # biases onto q, k, v; q and k rows divided by their root mean square
+            ops.bias_row_norm(proj, (0, k_col, v_col, v_col + self.kv_heads * self.vdim), self.qkv_bias, self.qk_gain,
+                              self.eps)
         if not self._plain:
             blend = None
             if self.value_mix == "first":

@@ -11,6 +11,8 @@
 * ``GatedMLP``: down(act(gate h) * (up h)) with the activation as a parameter
   (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), or ``silu``);
   the activation and the product are computed in float32 and rounded once.
+  ``swish_clamped`` (parameters ``limit`` L and ``slope`` a) clamps both inputs first,
+  g' = min(g, L), u' = clamp(u, -L, L), and gives g' sigmoid(a g') (u' + 1).
 """
 
 from __future__ import annotations
@@ -24,13 +26,15 @@ ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2}
 
 
 class ScaledEmbedding(Embedding):
-    """params: vocab, hidden, scale."""
+    """params: vocab, hidden, scale, copies (default 1: the row is written that many times side by side, the
+    equal streams that hyper-connections start from)."""
 
     def __init__(self, params):
         super().__init__(params)
         self.vocab = int(params["vocab"])
         self.hidden = int(params["hidden"])
         self.scale = float(params.get("scale", 1.0))
+        self.copies = int(params.get("copies", 1))
         self.table = None
 
     def tensor_specs(self):
@@ -40,7 +44,9 @@ class ScaledEmbedding(Embedding):
         self.table = tensors["table"]
 
     def forward(self, ctx):
-        return ctx.ops.embed_scaled(self.table, ctx.batch.tokens, ctx.batch.n_rows, self.scale)
+        if self.copies == 1:
+            return ctx.ops.embed_scaled(self.table, ctx.batch.tokens, ctx.batch.n_rows, self.scale)
+        return ctx.ops.embed_scaled(self.table, ctx.batch.tokens, ctx.batch.n_rows, self.scale, copies=self.copies)
 
 
 class WideRMSNorm(Norm):
@@ -95,15 +101,18 @@ class WideRMSNorm(Norm):
 
 
 class GatedMLP(FeedForward):
-    """params: hidden, intermediate, activation."""
+    """params: hidden, intermediate, activation; for "swish_clamped" also limit and slope."""
 
     def __init__(self, params):
         super().__init__(params)
         self.hidden = int(params["hidden"])
         self.intermediate = int(params["intermediate"])
         self.activation = str(params.get("activation", "silu"))
-        if self.activation not in ("silu", "gelu_tanh"):
+        if self.activation not in ("silu", "gelu_tanh", "swish_clamped"):
             raise ValueError(f"unknown activation '{self.activation}' for a gated feed-forward")
+        self.act_params = None
+        if self.activation == "swish_clamped":
+            self.act_params = (float(params["limit"]), float(params.get("slope", 1.702)))
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self):
@@ -116,7 +125,10 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down"].contiguous()
 
     def forward(self, ctx, h):
-        act = ctx.ops.gate_up_act(h, self.w_gate_up, self.intermediate, self.activation)
+        if self.act_params is None:
+            act = ctx.ops.gate_up_act(h, self.w_gate_up, self.intermediate, self.activation)
+        else:
+            act = ctx.ops.gate_up_act(h, self.w_gate_up, self.intermediate, self.activation, act_params=self.act_params)
         return ctx.ops.linear(act, self.w_down)
 
 

@@ -73,8 +73,10 @@ def checkpoint_shapes(folder) -> dict[str, tuple]:
     return shapes
 
 
-def read_checkpoint(folder, expected: dict, device, compute: torch.dtype, duplicates=None) -> dict[str, torch.Tensor]:
-    """expected: full tensor name -> TensorSpec. Returns name -> tensor on ``device``."""
+def read_checkpoint(folder, expected: dict, device, compute: torch.dtype, duplicates=None,
+                    ignored=()) -> dict[str, torch.Tensor]:
+    """expected: full tensor name -> TensorSpec. Returns name -> tensor on ``device``. ``ignored``: names that
+    may be present and are not read."""
     from safetensors import safe_open
 
     folder = Path(folder)
@@ -82,6 +84,7 @@ def read_checkpoint(folder, expected: dict, device, compute: torch.dtype, duplic
     if not shards:
         raise FileNotFoundError(f"no *.safetensors under {folder}")
     duplicates = dict(duplicates or {})
+    ignored = set(ignored)
     found: dict[str, torch.Tensor] = {}
     spare: dict[str, torch.Tensor] = {}
     unexpected, wrong_shape, other = [], {}, []
@@ -108,6 +111,8 @@ def read_checkpoint(folder, expected: dict, device, compute: torch.dtype, duplic
                     found[name] = t.to(device=device, dtype=keep).contiguous()
                 elif name in duplicates:
                     spare[name] = f.get_tensor(name)
+                elif name in ignored:
+                    continue
                 else:
                     unexpected.append(name)
     for name, tensor in spare.items():

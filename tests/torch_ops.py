@@ -181,8 +181,8 @@ def _act(z, name):
 
 
 class _WideOps:
-    def embed_scaled(self, table, tokens, n_rows, scale):
-        return table[tokens.long()].float() * scale
+    def embed_scaled(self, table, tokens, n_rows, scale, copies=1):
+        return (table[tokens.long()].float() * scale).repeat(1, copies)
 
     def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype, branch2=None, scale=1.0, gain2=None):
         s = x
@@ -194,13 +194,18 @@ class _WideOps:
         first = (n * (offset + gain.float())).to(out_dtype)
         return first if gain2 is None else (first, (n * (offset + gain2.float())).to(out_dtype))
 
-    def gate_up_act(self, h, w_gate_up, intermediate, activation):
-        gu = self.linear(h, w_gate_up).float()
-        return (_act(gu[:, :intermediate], activation) * gu[:, intermediate:2 * intermediate]).to(self.dtype)
+    def gate_up_act(self, h, w_gate_up, intermediate, activation, act_params=None):
+        return self.gated_act(self.linear(h, w_gate_up), intermediate, activation, act_params=act_params)
 
-    def gated_act(self, gu, intermediate, activation, row_gate_col=None):
+    def gated_act(self, gu, intermediate, activation, row_gate_col=None, act_params=None):
         g = gu.float()
-        out = _act(g[:, :intermediate], activation) * g[:, intermediate:2 * intermediate]
+        if activation == "swish_clamped":
+            limit, slope = act_params
+            a = torch.clamp(g[:, :intermediate], max=limit)
+            b = torch.clamp(g[:, intermediate:2 * intermediate], min=-limit, max=limit)
+            out = a * torch.sigmoid(slope * a) * (b + 1.0)
+        else:
+            out = _act(g[:, :intermediate], activation) * g[:, intermediate:2 * intermediate]
         if row_gate_col is not None:
             out = out * torch.sigmoid(g[:, row_gate_col:row_gate_col + 1])
         return out.to(gu.dtype)
@@ -223,12 +228,80 @@ class _WideOps:
         out[:, out_col:out_col + heads * n] = y.to(out.dtype)
         return out
 
-    def moe_route(self, x, w, b, top, gate_row=False):
+    def moe_route(self, x, w, b, top, gate_row=False, over_all=False):
         z = x.float() @ w.float().t()
         row_gate = torch.sigmoid(z[:, -1]) if gate_row else None
-        z = (z[:, :-1] if gate_row else z) + b.float()
+        z = z[:, :-1] if gate_row else z
+        if b is not None:
+            z = z + b.float()
         best = torch.topk(z, top, dim=-1)  # ties are not exercised: equal logits do not occur with random weights
+        if over_all:
+            return best.indices.to(torch.int32), torch.softmax(z, dim=-1).gather(1, best.indices), row_gate
         return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1), row_gate
+
+    # -- hyper-connections, the state-space mixer, biases and row norms of attention --------------------
+    def hyper_rmsnorm(self, x, branch, fold, read, gain, offset, eps, x_new, out_dtype):
+        S = read.shape[0]
+        rows, C = x.shape[0], x.shape[1] // S
+        X = x.view(rows, S, C)
+        if branch is not None:
+            M, b = fold[:S * S].view(S, S), fold[S * S:]
+            X = torch.einsum("st,rsc->rtc", M, X) + b[None, :, None] * branch.float()[:, None, :]
+            x_new.copy_(X.reshape(rows, S * C))
+        u = torch.einsum("s,rsc->rc", read, X)
+        n = u * torch.rsqrt((u * u).mean(dim=-1, keepdim=True) + eps)
+        return (n * (offset + gain.float())).to(out_dtype)
+
+    def bias_row_norm(self, proj, cols, bias, gain, eps):
+        q0, k0, v0, end = cols
+        x = proj[:, q0:end].float()
+        if bias is not None:
+            x = x + bias
+        if gain is not None:
+            for a, b in ((q0, k0), (k0, v0)):
+                seg = x[:, a - q0:b - q0]
+                x[:, a - q0:b - q0] = seg * torch.rsqrt((seg * seg).mean(dim=-1, keepdim=True) + eps) * gain[a - q0:b - q0]
+        proj[:, q0:end] = x.to(proj.dtype)
+
+    def causal_conv_silu(self, x, w, b, tail, batch):
+        rows, ch = x.shape
+        taps = w.shape[1]
+        out = torch.empty((rows, ch), dtype=torch.float32)
+        row0 = 0
+        for slot, n in zip(batch.slots, batch.q_lens):
+            seq = torch.cat([tail[slot][-(taps - 1):].float(), x[row0:row0 + n].float()]) if taps > 1 else x[row0:row0 + n].float()
+            acc = b.float()[None, :].repeat(n, 1)
+            for j in range(taps):
+                acc += seq[j:j + n] * w[:, j].float()
+            out[row0:row0 + n] = acc
+            if taps > 1:
+                tail[slot][-(taps - 1):] = seq[n:].to(tail.dtype)
+            row0 += n
+        return (out * torch.sigmoid(out)).to(x.dtype)
+
+    def ssd_scan(self, x, B, C, dt, dt_bias, a_log, skip, heads, P, N, groups, state, batch):
+        rows = x.shape[0]
+        xf, Bf, Cf = x.float().reshape(rows, heads, P), B.float().reshape(rows, groups, N), C.float().reshape(rows, groups, N)
+        step = torch.nn.functional.softplus(dt.float() + dt_bias, threshold=30.0)
+        decay = torch.exp(-torch.exp(a_log) * step)
+        g_of = torch.arange(heads) // (heads // groups)
+        y = torch.empty((rows, heads, P), dtype=torch.float32)
+        row0 = 0
+        for slot, n in zip(batch.slots, batch.q_lens):
+            S = state[slot].clone()  # [heads, N, P]
+            for t in range(row0, row0 + n):
+                S = decay[t][:, None, None] * S + step[t][:, None, None] * Bf[t][g_of][:, :, None] * xf[t][:, None, :]
+                y[t] = torch.einsum("hn,hnp->hp", Cf[t][g_of], S) + skip[:, None] * xf[t]
+            state[slot] = S
+            row0 += n
+        return y.reshape(rows, heads * P)
+
+    def gated_group_norm(self, y, gate_rows, weight, parts, eps, out, out_col, out_scale):
+        rows, inner = y.shape
+        z = gate_rows.float()
+        v = (y * (z * torch.sigmoid(z))).view(rows, parts, inner // parts)
+        v = v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps)
+        out[:, out_col:out_col + inner] = (v.reshape(rows, inner) * weight * out_scale).to(out.dtype)
 
     def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, add_gate=None,
                     batch=None):
