@@ -52,9 +52,11 @@ _SIGNATURES = {
     "krk_lt_gemm_report": [_P, _P],
 }
 _MIX_SIGNATURES = {
-    "krk_embed_scaled": [_P, _P, _P, c_int, c_int, c_int, c_float, _P, c_int, _P],
+    "krk_embed_scaled": [_P, _P, _P, c_int, c_int, c_int, c_float, _P, c_int, _P, c_int],
     "krk_rmsnorm_wide": [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_float, _P, c_float, _P, _P, c_int, _P],
-    "krk_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_float, c_float],
+    "krk_hyper_rmsnorm": [_P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_float, c_int, _P],
+    "krk_bias_row_norm": [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, c_int, c_int, _P],
     "krk_rotate_norm_write": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, _P, _P,
                               _P, _P, c_int, _P, _P, c_int, c_int, _P, c_int, c_float, c_int, _P],
     "krk_sink_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
@@ -66,7 +68,7 @@ _MIX_SIGNATURES = {
     "krk_head_linear": [_P, c_int, c_int, c_float, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
 }
 _MOE_SIGNATURES = {
-    "krk_moe_route": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_route": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_int],
     "krk_moe_gate_up_pairs": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_moe_down_pairs": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_moe_sort": [_P, _P, _P, c_int, c_int, c_int, _P],
@@ -78,8 +80,12 @@ _SCAN_SIGNATURES = {
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
                               c_int, _P, _P, _P, c_int, _P, _P, c_int, _P],
+    "krk_causal_conv_silu": [_P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P],
+    "krk_ssd_scan": [_P, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                     c_int, _P, _P, _P, c_int, _P, _P, c_int, _P],
+    "krk_gated_group_norm": [_P, c_int, c_int, c_float, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, _P],
 }
-_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2}
+_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2, "swish_clamped": 3}
 _ATTN_SIGNATURES = {
     "krk_attention_simple": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
     "krk_attention_head_dim": [],
@@ -497,12 +503,42 @@ class Kernels:
             raise KernelError("a kernel input must be a 2-D tensor (or column slice) with contiguous rows")
         return t.data_ptr(), t.stride(0)
 
-    def embed_scaled(self, table, tokens, n_rows, scale):
-        out = torch.empty((n_rows, table.shape[1]), dtype=torch.float32, device=table.device)
+    def embed_scaled(self, table, tokens, n_rows, scale, copies=1):
+        """float32 rows table[token] * scale, each written ``copies`` times side by side."""
+        out = torch.empty((n_rows, copies * table.shape[1]), dtype=torch.float32, device=table.device)
         self._ok(self.mix.krk_embed_scaled(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), n_rows, table.shape[1],
                                            table.shape[0], float(scale), self.error.data_ptr(), _code(table.dtype),
-                                           self._stream()), "scaled embedding gather")
+                                           self._stream(), int(copies)), "scaled embedding gather")
         return out
+
+    def hyper_rmsnorm(self, x, branch, fold, read, gain, offset, eps, x_new, out_dtype):
+        """Rows of S float32 streams side by side. With a pending ``branch``, the streams are rewritten into ``x_new``
+        through ``fold`` (M [S, S] indexed [from, to], then b [S]): x_t = sum_s M[s, t] x_s + b_t * branch. Returns
+        norm(sum_s read[s] x_s) * (offset + gain) in ``out_dtype``."""
+        S = read.shape[0]
+        rows, C = x.shape[0], x.shape[1] // S
+        if x.dtype != torch.float32 or not x.is_contiguous() or gain.dtype != torch.float32 or gain.shape[0] != C:
+            raise KernelError("the hyper-connection norm reads contiguous float32 streams and a float32 gain")
+        if branch is not None and (branch.dtype != out_dtype or not branch.is_contiguous() or branch.shape != (rows, C)
+                                   or fold is None or fold.numel() != S * S + S):
+            raise KernelError("the pending output must have the path's dtype and one stream's shape, with its M and b")
+        out = torch.empty((rows, C), dtype=out_dtype, device=x.device)
+        self._ok(self.mix.krk_hyper_rmsnorm(out.data_ptr(), x_new.data_ptr() if branch is not None else None, x.data_ptr(),
+                                            _ptr(branch), _ptr(fold) if branch is not None else None, read.data_ptr(),
+                                            gain.data_ptr(), float(offset), rows, S, C, float(eps), _code(out_dtype),
+                                            self._stream()), "hyper-connection rmsnorm")
+        return out
+
+    def bias_row_norm(self, proj, cols, bias, gain, eps):
+        """In place on a stacked q | k | v product: ``cols`` = (q0, k0, v0, end) column bounds; float32 ``bias`` over
+        q0..end is added (None: none), and with ``gain`` (float32 over q0..v0) the q columns and the k columns are each
+        divided by their root mean square and multiplied by it."""
+        ptr, stride = self._rows_view(proj)
+        q0, k0, v0, end = (int(c) for c in cols)
+        if (bias is not None and bias.numel() != end - q0) or (gain is not None and gain.numel() != v0 - q0):
+            raise KernelError("bias and gain must cover the columns they are applied to")
+        self._ok(self.mix.krk_bias_row_norm(ptr, stride, q0, k0, v0, end, _ptr(bias), _ptr(gain), float(eps), proj.shape[0],
+                                            _code(proj.dtype), self._stream()), "projection biases + row norms")
 
     def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype, branch2=None, scale=1.0, gain2=None):
         """Rows of a float32 stream, normalised into ``out_dtype``; with a branch, ``x_new`` = x + scale * (branch +
@@ -522,13 +558,17 @@ class Kernels:
                                            self._stream()), "wide rmsnorm")
         return out if gain2 is None else (out, out2)
 
-    def gated_act(self, gu, intermediate, activation, row_gate_col=None):
-        """act(gu[:, :I]) * gu[:, I:2I], times sigmoid(gu[:, row_gate_col]) per row if that column is given."""
+    def gated_act(self, gu, intermediate, activation, row_gate_col=None, act_params=None):
+        """act(gu[:, :I]) * gu[:, I:2I], times sigmoid(gu[:, row_gate_col]) per row if that column is given.
+        "swish_clamped" takes ``act_params`` = (limit, slope)."""
         ptr, stride = self._rows_view(gu)
         out = torch.empty((gu.shape[0], intermediate), dtype=gu.dtype, device=gu.device)
+        limit, slope = act_params if act_params is not None else (0.0, 1.0)
+        if activation == "swish_clamped" and act_params is None:
+            raise KernelError("the clamped activation needs its limit and slope")
         self._ok(self.mix.krk_gated_act(out.data_ptr(), ptr, stride, gu.shape[0], intermediate, _ACTIVATIONS[activation],
                                         -1 if row_gate_col is None else int(row_gate_col), _code(gu.dtype),
-                                        self._stream()), "gated activation")
+                                        self._stream(), float(limit), float(slope)), "gated activation")
         return out
 
     def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache, keep_rows=False):
@@ -571,10 +611,11 @@ class Kernels:
     # -- routed experts ------------------------------------------------------------------------
     MOE_PAIR_ROWS = 16  # rows up to which every (row, expert) pair reads its expert's weights by itself
 
-    def moe_route(self, x, w, b, top, gate_row=False):
+    def moe_route(self, x, w, b, top, gate_row=False, over_all=False):
         """(experts int32 [rows, top], weights float32 [rows, top], row gate float32 [rows] or None): the ``top`` largest
-        of x W^T + b in 32-bit (ties: the lower index) and the softmax over them. With ``gate_row`` the last row of W is
-        no expert but a gate's weights: sigmoid of its product is the row gate."""
+        of x W^T + b in 32-bit (ties: the lower index) and the softmax over them, or with ``over_all`` their shares of
+        the softmax over all experts. With ``gate_row`` the last row of W is no expert but a gate's weights: sigmoid
+        of its product is the row gate."""
         E = w.shape[0] - int(gate_row)
         rows, K = x.shape
         experts = torch.empty((rows, top), dtype=torch.int32, device=x.device)
@@ -582,7 +623,7 @@ class Kernels:
         row_gate = torch.empty(rows, dtype=torch.float32, device=x.device) if gate_row else None
         logits = self.linear(x, w, out_float32=True)
         self._ok(self.moe.krk_moe_route(experts.data_ptr(), weights.data_ptr(), _ptr(row_gate), logits.data_ptr(), _ptr(b),
-                                        rows, E, int(gate_row), int(top), self._stream()), "expert routing")
+                                        rows, E, int(gate_row), int(top), self._stream(), int(over_all)), "expert routing")
         return experts, weights, row_gate
 
     def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, add_gate=None,
@@ -638,8 +679,10 @@ class Kernels:
                                           self._stream()), "experts' sum")
         return out
 
-    def gate_up_act(self, h, w_gate_up, intermediate, activation):
+    def gate_up_act(self, h, w_gate_up, intermediate, activation, act_params=None):
         """act(gate h) * (up h) with W = cat(gate, up); silu on few bfloat16 rows runs in the product's epilogue."""
+        if act_params is not None:
+            return self.gated_act(self.linear(h, w_gate_up), intermediate, activation, act_params=act_params)
         if activation == "silu" and self._use_skinny(h, w_gate_up):
             return self.gate_up_swiglu(h, w_gate_up, intermediate)
         if activation == "gelu_tanh" and self._use_skinny(h, w_gate_up):  # few rows: in the product's epilogue
@@ -773,6 +816,60 @@ class Kernels:
             lora.shape[1], batch.n_seqs, batch.cu_q.data_ptr(), batch.seq_qlen.data_ptr(), batch.seq_slot.data_ptr(),
             rows, _ptr(prep), _ptr(o_raw), _code(r.dtype), self._stream())
         self._ok(rc, f"{kind} recurrence (heads of up to 256 channels)")
+
+    # -- state-space mixer ------------------------------------------------------------------
+    SSD_CHUNK = 128  # tokens per chunk where one sequence's step is long enough to be scanned in chunks
+
+    def causal_conv_silu(self, x, w, b, tail, batch):
+        """silu(b + short causal convolution over each sequence's rows); ``tail`` [slots, taps - 1, channels] holds
+        every sequence's last inputs and is brought up to date. x may be a column slice; w [channels, taps] float32."""
+        ptr, stride = self._rows_view(x)
+        rows, ch = x.shape
+        taps = w.shape[1]
+        if tail.dtype != x.dtype or not tail.is_contiguous() or tail.shape[1:] != (max(taps - 1, 1), ch):
+            raise KernelError("the convolution's stored inputs have the path's dtype and [taps - 1, channels] per slot")
+        out = torch.empty((rows, ch), dtype=x.dtype, device=x.device)
+        self._ok(self.scan.krk_causal_conv_silu(out.data_ptr(), ptr, stride, w.data_ptr(), b.data_ptr(), tail.data_ptr(),
+                                               taps, ch, rows, batch.n_seqs, batch.row_seq.data_ptr(),
+                                               batch.cu_q.data_ptr(), batch.seq_qlen.data_ptr(), batch.seq_slot.data_ptr(),
+                                               _code(x.dtype), self._stream()), "causal convolution + silu")
+        self.launches += int(taps > 1)
+        return out
+
+    def ssd_scan(self, x, B, C, dt, dt_bias, a_log, skip, heads, P, N, groups, state, batch):
+        """The scan of a state-space mixer over a step's rows (csrc/ssd.cu): float32 y [rows, heads * P]; ``state``
+        [slots, heads, N, P] float32 is read and left as the sequences' new state."""
+        views = [self._rows_view(t) for t in (x, B, C, dt)]
+        rows = x.shape[0]
+        if state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1:] != (heads, N, P):
+            raise KernelError("the scan keeps a contiguous float32 state [slots, heads, N, P]")
+        y = torch.empty((rows, heads * P), dtype=torch.float32, device=x.device)
+        chunk, cs, cd = 0, None, None
+        if not batch.is_decode and batch.max_q_len >= 2 * self.SSD_CHUNK:
+            chunk = self.SSD_CHUNK
+            n_chunks = -(-batch.max_q_len // chunk)
+            cs = torch.empty((batch.n_seqs * n_chunks * heads, N * P), dtype=torch.float32, device=x.device)
+            cd = torch.empty(batch.n_seqs * n_chunks * heads, dtype=torch.float32, device=x.device)
+            self.launches += 2
+        self._ok(self.scan.krk_ssd_scan(y.data_ptr(), views[0][0], views[0][1], views[1][0], views[1][1], views[2][0],
+                                        views[2][1], views[3][0], views[3][1], dt_bias.data_ptr(), a_log.data_ptr(),
+                                        skip.data_ptr(), state.data_ptr(), heads, P, N, groups, batch.n_seqs,
+                                        batch.max_q_len, batch.cu_q.data_ptr(), batch.seq_qlen.data_ptr(),
+                                        batch.seq_slot.data_ptr(), chunk, _ptr(cs), _ptr(cd), _code(x.dtype),
+                                        self._stream()), "state-space scan (a head's state must fit a block's registers)")
+        return y
+
+    def gated_group_norm(self, y, gate_rows, weight, parts, eps, out, out_col, out_scale):
+        """out[:, out_col:...] = group_norm(y * silu(gate_rows)) * weight * out_scale; y float32, ``parts`` equal parts
+        each divided by its own root mean square."""
+        zptr, zstride = self._rows_view(gate_rows)
+        optr, ostride = self._rows_view(out)
+        rows, inner = y.shape
+        if y.dtype != torch.float32 or not y.is_contiguous() or gate_rows.dtype != out.dtype:
+            raise KernelError("the gated norm reads float32 rows and a gate of the path's dtype")
+        self._ok(self.scan.krk_gated_group_norm(optr, ostride, int(out_col), float(out_scale), y.data_ptr(), zptr, zstride,
+                                               weight.data_ptr(), rows, inner, int(parts), float(eps), _code(out.dtype),
+                                               self._stream()), "gated group norm")
 
     # -- token selection ------------------------------------------------------------
     def select_tokens(self, logits, temperature, seed, requests, step, feed=None, out=None):

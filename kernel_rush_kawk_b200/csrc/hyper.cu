@@ -1,0 +1,140 @@
+// Row kernels of models with several residual streams (hyper-connections), and the biases and whole-row norms
+// of an attention's projections.
+//
+// krk_hyper_rmsnorm: a token's S streams lie side by side in one float32 row [S * C]. With a pending output y
+// [C] of the sublayer before and that sublayer's M [S, S] (indexed [from, to]) and b [S], the streams are
+// rewritten, all from the old ones, x_t <- sum_s M[s, t] x_s + b_t y, and stored. Then u = sum_s a_s x_s with
+// the next sublayer's a [S], and out = u * rsqrt(mean(u^2) + eps) * (offset + gain), rounded once to the
+// path's type. Everything else is float32. One block per row; u is held in shared memory.
+//
+// krk_bias_row_norm: in place on the rows of a stacked q | k | v product: the biases are added, the q columns
+// (all heads together) are divided by their root mean square and multiplied by a weight of their size, the k
+// columns likewise, in float32, and the row is rounded back to the path's type.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void hyper_rmsnorm_kernel(T* __restrict__ out, float* x_new, const float* x, const T* __restrict__ branch,
+                                     const float* __restrict__ fold, const float* __restrict__ read,
+                                     const float* __restrict__ gain, float offset, int S, int C, float eps) {
+  extern __shared__ __align__(16) float u_s[];  // C floats
+  __shared__ float scratch[32];
+  __shared__ float w_s[MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS];
+  grid_launch_dependents();
+  float* M = w_s;                  // [from][to]
+  float* b = w_s + S * S;          // [to]
+  float* a = w_s + S * S + S;      // [from]
+  if (threadIdx.x < S * S + S) w_s[threadIdx.x] = branch ? fold[threadIdx.x] : 0.f;  // weights: no kernel writes them
+  if (threadIdx.x < S) a[threadIdx.x] = read[threadIdx.x];
+  __syncthreads();
+  grid_dependency_wait();
+  const size_t base = (size_t)blockIdx.x * S * C;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float xs[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; ++s)
+      if (s < S) xs[s] = x[base + (size_t)s * C + c];
+    float u = 0.f;
+    if (branch) {
+      const float y = to_float<T>(branch[(size_t)blockIdx.x * C + c]);
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t) {
+        if (t < S) {
+          float v = 0.f;
+#pragma unroll
+          for (int s = 0; s < MAX_STREAMS; ++s)
+            if (s < S) v += M[s * S + t] * xs[s];
+          v += b[t] * y;
+          x_new[base + (size_t)t * C + c] = v;
+          u += a[t] * v;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < S) u += a[s] * xs[s];
+    }
+    u_s[c] = u;
+    sq += u * u;
+  }
+  const float rstd = rsqrtf(block_sum(sq, scratch) / (float)C + eps);
+  for (int c = threadIdx.x; c < C; c += blockDim.x)
+    out[(size_t)blockIdx.x * C + c] = from_float<T>(u_s[c] * rstd * (offset + gain[c]));
+}
+
+// one block per row; columns q0 .. k0 are the q row, k0 .. v0 the k row, v0 .. end the v row
+template <typename T>
+__global__ void bias_row_norm_kernel(T* proj, int stride, int q0, int k0, int v0, int end,
+                                     const float* __restrict__ bias, const float* __restrict__ gain, float eps) {
+  extern __shared__ __align__(16) float row_s[];  // end - q0 floats
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  T* row = proj + (size_t)blockIdx.x * stride + q0;
+  const int nq = k0 - q0, nk = v0 - k0, n = end - q0;
+  float sq_q = 0.f, sq_k = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = to_float<T>(row[i]) + (bias ? bias[i] : 0.f);
+    row_s[i] = v;
+    if (i < nq) sq_q += v * v;
+    else if (i < nq + nk) sq_k += v * v;
+  }
+  float rq = 1.f, rk = 1.f;
+  if (gain) {
+    rq = rsqrtf(block_sum(sq_q, scratch) / (float)nq + eps);
+    rk = rsqrtf(block_sum(sq_k, scratch) / (float)nk + eps);
+  } else {
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = row_s[i];
+    if (gain && i < nq + nk) v *= (i < nq ? rq : rk) * gain[i];
+    row[i] = from_float<T>(v);
+  }
+}
+
+}  // namespace
+
+KRK_API int krk_hyper_rmsnorm(void* out, float* x_new, const float* x, const void* branch, const float* fold,
+                              const float* read, const float* gain, float offset, int rows, int S, int C, float eps,
+                              int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (S < 1 || S > MAX_STREAMS || (branch && !fold)) return -2;
+  const size_t smem = (size_t)C * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  const int threads = C >= 4096 ? 512 : (C >= 1024 ? 256 : 128);
+  if (dtype == KRK_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(hyper_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(hyper_rmsnorm_kernel<float>, dim3(rows), dim3(threads), smem, stream, (float*)out, x_new, x,
+                           (const float*)branch, fold, read, gain, offset, S, C, eps);
+  }
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(hyper_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(hyper_rmsnorm_kernel<bf16>, dim3(rows), dim3(threads), smem, stream, (bf16*)out, x_new, x,
+                         (const bf16*)branch, fold, read, gain, offset, S, C, eps);
+}
+
+KRK_API int krk_bias_row_norm(void* proj, int stride, int q0, int k0, int v0, int end, const float* bias,
+                              const float* gain, float eps, int rows, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (!(q0 < k0 && k0 < v0 && v0 <= end)) return -2;
+  const int n = end - q0;
+  const size_t smem = (size_t)n * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  const int threads = n >= 4096 ? 512 : (n >= 1024 ? 256 : 128);
+  if (dtype == KRK_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(bias_row_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(bias_row_norm_kernel<float>, dim3(rows), dim3(threads), smem, stream, (float*)proj, stride, q0,
+                           k0, v0, end, bias, gain, eps);
+  }
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(bias_row_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(bias_row_norm_kernel<bf16>, dim3(rows), dim3(threads), smem, stream, (bf16*)proj, stride, q0, k0,
+                         v0, end, bias, gain, eps);
+}

@@ -1,7 +1,8 @@
 // Kernels of a feed-forward of routed experts.
 //
 // krk_moe_route: one warp per row. z = logits[r, :] + bias (float32); the `top` largest are taken one after
-// the other (ties: the lower index), and their weights are the softmax over the chosen logits alone. A gate of one
+// the other (ties: the lower index), and their weights are the softmax over the chosen logits alone, or
+// (`over_all`) each chosen expert's share of the softmax over all experts, which do not sum to one. A gate of one
 // number per row may ride in the router's product as its last column: sigmoid of it is written beside the routing and
 // multiplies what the experts' sum is added onto (a shared expert's output). (The router's product inside this
 // kernel, one block per row, was measured for single-token steps and lost to the product kernel before it: 1.72
@@ -32,9 +33,17 @@ constexpr int ROUTE_WARPS = 4;
 // One warp: the `top` largest of z[0..E) one after the other (z is the warp's own shared memory and is consumed),
 // their softmax weights.
 __device__ __forceinline__ void route_row(float* z, int E, int top, int lane, int* __restrict__ experts,
-                                          float* __restrict__ weights) {
+                                          float* __restrict__ weights, int over_all) {
   float first = 0.f, total = 0.f, mine = 0.f;
   int mine_e = 0;
+  float all = 0.f;
+  if (over_all) {  // the denominator over every expert, before the walk consumes z
+    float big = -INFINITY;
+    for (int e = lane; e < E; e += 32) big = fmaxf(big, z[e]);
+    big = warp_max(big);
+    for (int e = lane; e < E; e += 32) all += expf(z[e] - big);
+    all = warp_sum(all);
+  }
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -57,7 +66,7 @@ __device__ __forceinline__ void route_row(float* z, int E, int top, int lane, in
   }
   if (lane < top) {
     experts[lane] = mine_e;
-    weights[lane] = mine / total;
+    weights[lane] = mine / (over_all ? all : total);  // the largest logit is the first one taken
   }
 }
 
@@ -65,7 +74,7 @@ __device__ __forceinline__ void route_row(float* z, int E, int top, int lane, in
 // product), and sigmoid of it goes to row_gate
 __global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ weights, float* __restrict__ row_gate,
                                  const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E,
-                                 int has_gate, int top) {
+                                 int has_gate, int top, int over_all) {
   extern __shared__ float z_s[];  // [warps][E]
   grid_launch_dependents();
   grid_dependency_wait();
@@ -77,7 +86,7 @@ __global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ 
   for (int e = lane; e < E; e += 32) z[e] = src[e] + (bias ? bias[e] : 0.f);
   if (has_gate && lane == 0) row_gate[row] = act_of(src[E], 2);
   __syncwarp();
-  route_row(z, E, top, lane, experts + (size_t)row * top, weights + (size_t)row * top);
+  route_row(z, E, top, lane, experts + (size_t)row * top, weights + (size_t)row * top, over_all);
 }
 
 constexpr int PAIR_WARPS = 8;
@@ -235,13 +244,13 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ad
 }  // namespace
 
 KRK_API int krk_moe_route(int* experts, float* weights, float* row_gate, const float* logits, const float* bias, int rows,
-                          int E, int has_gate, int top, cudaStream_t stream) {
+                          int E, int has_gate, int top, cudaStream_t stream, int over_all) {
   if (rows == 0) return 0;
   if (top < 1 || top > 32 || top > E) return -2;
   const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
   if (smem > 48 * 1024) return -2;
   return (int)launch_pdl(moe_route_kernel, dim3((rows + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream,
-                         experts, weights, row_gate, logits, bias, rows, E, has_gate, top);
+                         experts, weights, row_gate, logits, bias, rows, E, has_gate, top, over_all);
 }
 
 KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, const void* w, const int* experts, int rows,

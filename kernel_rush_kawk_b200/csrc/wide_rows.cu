@@ -13,7 +13,7 @@ namespace {
 
 template <typename T>
 __global__ void embed_scaled_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
-                                    int H, int n_table_rows, float scale, int* error) {
+                                    int H, int n_table_rows, float scale, int* error, int copies) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int r = blockIdx.x;
@@ -21,8 +21,11 @@ __global__ void embed_scaled_kernel(float* __restrict__ out, const T* __restrict
   const bool bad = id < 0 || id >= n_table_rows;
   if (bad && threadIdx.x == 0 && error) atomicExch(error, 1);
   const T* src = table + (size_t)(bad ? 0 : id) * H;
-  float* dst = out + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = bad ? 0.f : to_float<T>(src[i]) * scale;
+  float* dst = out + (size_t)r * H * copies;  // the row is written `copies` times side by side
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = bad ? 0.f : to_float<T>(src[i]) * scale;
+    for (int c = 0; c < copies; ++c) dst[(size_t)c * H + i] = v;
+  }
 }
 
 template <typename T> __device__ __forceinline__ void load4_rows(const T* p, float* f);
@@ -119,11 +122,20 @@ __device__ __forceinline__ float activation(float z, int act) {
   return 1.0f / (1.0f + expf(-z));                                                              // sigmoid
 }
 
+// act 3: both inputs are clamped first, g' = min(g, limit), u' = clamp(u, -limit, limit), and the result is
+// g' * sigmoid(slope * g') * (u' + 1)
+__device__ __forceinline__ float gated(float g, float u, int act, float limit, float slope) {
+  if (act != 3) return activation(g, act) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
+
 // out[r, i] = round(act(g) * u), g = gu[r, i], u = gu[r, I + i]; with row_gate_col >= 0 the row is also
 // multiplied by sigmoid(gu[r, row_gate_col]) (a gate of one number per row that rides in the same product)
 template <typename T, bool VEC>
 __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int gu_stride, int I, int act,
-                                 int row_gate_col) {
+                                 int row_gate_col, float limit, float slope) {
   grid_launch_dependents();
   grid_dependency_wait();
   const size_t r = blockIdx.x;
@@ -134,7 +146,7 @@ __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, 
       load4_rows<T>(gu + r * gu_stride + i, g);
       load4_rows<T>(gu + r * gu_stride + I + i, u);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = activation(g[j], act) * u[j] * rg;
+      for (int j = 0; j < 4; ++j) o[j] = gated(g[j], u[j], act, limit, slope) * rg;
       store4_rows<T>(out + r * I + i, o);
     }
     return;
@@ -142,20 +154,21 @@ __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, 
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
     const float g = to_float<T>(gu[r * gu_stride + i]);
     const float u = to_float<T>(gu[r * gu_stride + I + i]);
-    out[r * I + i] = from_float<T>(activation(g, act) * u * rg);
+    out[r * I + i] = from_float<T>(gated(g, u, act, limit, slope) * rg);
   }
 }
 
 }  // namespace
 
 KRK_API int krk_embed_scaled(float* out, const void* table, const int* ids, int rows, int H, int n_table_rows, float scale,
-                             int* error, int dtype, cudaStream_t stream) {
+                             int* error, int dtype, cudaStream_t stream, int copies) {
   if (rows == 0) return 0;
+  if (copies < 1) return -2;
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(embed_scaled_kernel<float>, dim3(rows), dim3(128), 0, stream, out, (const float*)table, ids, H,
-                           n_table_rows, scale, error);
+                           n_table_rows, scale, error, copies);
   return (int)launch_pdl(embed_scaled_kernel<bf16>, dim3(rows), dim3(128), 0, stream, out, (const bf16*)table, ids, H,
-                         n_table_rows, scale, error);
+                         n_table_rows, scale, error, copies);
 }
 
 template <typename T>
@@ -183,14 +196,14 @@ KRK_API int krk_rmsnorm_wide(void* out, float* x_new, const float* x, const void
 }
 
 KRK_API int krk_gated_act(void* out, const void* gu, int gu_stride, int rows, int I, int act, int row_gate_col, int dtype,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, float limit, float slope) {
   if (rows == 0) return 0;
   const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
   const bool vec = I % 4 == 0 && gu_stride % 4 == 0 && ((uintptr_t)gu & (4 * esz - 1)) == 0;
   const int chunks = min(64, (I / (vec ? 4 : 1) + 255) / 256);
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(vec ? gated_act_kernel<float, true> : gated_act_kernel<float, false>, dim3(rows, chunks),
-                           dim3(256), 0, stream, (float*)out, (const float*)gu, gu_stride, I, act, row_gate_col);
+                           dim3(256), 0, stream, (float*)out, (const float*)gu, gu_stride, I, act, row_gate_col, limit, slope);
   return (int)launch_pdl(vec ? gated_act_kernel<bf16, true> : gated_act_kernel<bf16, false>, dim3(rows, chunks), dim3(256),
-                         0, stream, (bf16*)out, (const bf16*)gu, gu_stride, I, act, row_gate_col);
+                         0, stream, (bf16*)out, (const bf16*)gu, gu_stride, I, act, row_gate_col, limit, slope);
 }
