@@ -185,6 +185,8 @@ def layer_runs(cfg):
 
 def sublayer(X, w, p, q, f, gain, eps):
     """X [S, T, C] -> the new streams after sublayer q ("hc1" or "hc2") whose function is f."""
+    if p + q + ".in" not in w:  # one stream without hyper-connection weights: the plain residual sum
+        return X + f(rms_norm(X[0], gain, eps))[None]
     a, b, M = w[p + q + ".in"], w[p + q + ".out"], w[p + q + ".mix"]
     u = torch.einsum("s,stc->tc", a, X)
     y = f(rms_norm(u, gain, eps))
