@@ -31,6 +31,12 @@ tokens, attention over one cached low-rank row per token, routed experts with a 
 Qwen3 twin has the same width, head count and head size, and a feed-forward as wide as what one token runs
 through (chosen experts plus the shared one).
 
+``--only design_zadunex`` measures the Zadunex decoder (state-space layers with a matrix state per head, attention
+with biases, row norms and a sink, hyper-connections over two residual streams, clamped dense and routed
+feed-forwards) at two sizes beside its closest existing model, the Taredra hybrid decoder of equal width,
+feed-forward, heads and layer count (recurrent layers beside attention, a 32-bit stream), and beside the Qwen3
+decoder of that size.
+
 ``--only workload_8b`` and ``--only workload_14b`` run the baseline's two larger
 configurations (Qwen3-8B sizes: 8 prompts of 256 to 2,048 tokens, 128 greedy steps;
 Qwen3-14B sizes: 16 prompts of 512 to 4,096 tokens, 128 steps at temperature 0.7)
@@ -206,13 +212,20 @@ DESIGN_SIZES = {
                       "head_dim": 128, "vocab_size": 32768},
     "disorax_lite": {"hidden_size": 2048, "intermediate_size": 11264, "num_attention_heads": 16, "num_key_value_heads": 4,
                      "head_dim": 128, "vocab_size": 32768},
+    "zadunex_1b": {"hidden_size": 1536, "intermediate_size": 6144, "num_attention_heads": 12, "num_key_value_heads": 4,
+                   "head_dim": 128, "vocab_size": 32768},
+    "zadunex_4b": {"hidden_size": 2560, "intermediate_size": 9728, "num_attention_heads": 32, "num_key_value_heads": 8,
+                   "head_dim": 128, "vocab_size": 32768},
 }
+#: a design's closest existing model of equal size, measured beside it as well (preset -> preset)
+DESIGN_NEIGHBOURS = {"zadunex_1b": "taredra_1b", "zadunex_4b": "taredra_4b"}
 KERNEL_FAMILIES = {
     "product": ("_skinny", "_library_gemm", "_gemm_nt", "gemm_tcgen05"),
-    "norm": ("rmsnorm", "add_rmsnorm", "rmsnorm_wide"),
+    "norm": ("rmsnorm", "add_rmsnorm", "rmsnorm_wide", "hyper_rmsnorm"),
     "activation": ("swiglu", "gated_act"),
-    "attention": ("rope_attention", "rotate_norm_write", "sink_attention", "latent_norm_write", "head_linear"),
-    "recurrence": ("token_shift", "linear_recurrence"),
+    "attention": ("rope_attention", "rotate_norm_write", "sink_attention", "latent_norm_write", "head_linear",
+                  "bias_row_norm"),
+    "recurrence": ("token_shift", "linear_recurrence", "causal_conv_silu", "ssd_scan", "gated_group_norm"),
     # routing and the routed experts; for steps of many tokens this holds the experts' dense products too, which
     # the product family counts as well
     "experts": ("moe_route", "moe_experts"),
@@ -325,8 +338,12 @@ def run_designs(args) -> dict:
         t_cfg = type(t_cfg).from_dict({**t_cfg.to_dict(), "layers": t_cfg.to_dict()["layers"][:layers]})
         q_cfg = Qwen3Config.from_dict({**twin, "num_hidden_layers": layers, "rms_norm_eps": 1e-6, "rope_theta": 1e4,
                                        "tie_word_embeddings": True, "max_position_embeddings": CONTEXT})
-        out["sizes"][preset] = {"layers": layers, design: measure(t_cfg, t_cfg.vocab),
-                                "qwen3": measure(q_cfg, q_cfg.vocab_size)}
+        out["sizes"][preset] = {"layers": layers, design: measure(t_cfg, t_cfg.vocab)}
+        if preset in DESIGN_NEIGHBOURS:
+            n_cfg = preset_config(DESIGN_NEIGHBOURS[preset])
+            n_cfg = type(n_cfg).from_dict({**n_cfg.to_dict(), "layers": n_cfg.to_dict()["layers"][:layers]})
+            out["sizes"][preset][DESIGN_NEIGHBOURS[preset]] = measure(n_cfg, n_cfg.vocab)
+        out["sizes"][preset]["qwen3"] = measure(q_cfg, q_cfg.vocab_size)
     return out
 
 
@@ -636,7 +653,8 @@ def main() -> int:
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64",
-                                                  "workload_8b", "workload_14b", "design_taredra", "design_disorax"],
+                                                  "workload_8b", "workload_14b", "design_taredra", "design_disorax",
+                                                  "design_zadunex"],
                    help="run one piece only (for profiling), or one of the baseline's larger configurations end to end")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()

@@ -822,10 +822,12 @@ class Kernels:
 
     def causal_conv_silu(self, x, w, b, tail, batch):
         """silu(b + short causal convolution over each sequence's rows); ``tail`` [slots, taps - 1, channels] holds
-        every sequence's last inputs and is brought up to date. x may be a column slice; w [channels, taps] float32."""
+        every sequence's last inputs and is brought up to date. x may be a column slice; w [taps, channels] float32."""
         ptr, stride = self._rows_view(x)
         rows, ch = x.shape
-        taps = w.shape[1]
+        taps = w.shape[0]
+        if w.shape[1] != ch or not w.is_contiguous():
+            raise KernelError("the convolution's weights come tap-major, [taps, channels], contiguous")
         if tail.dtype != x.dtype or not tail.is_contiguous() or tail.shape[1:] != (max(taps - 1, 1), ch):
             raise KernelError("the convolution's stored inputs have the path's dtype and [taps - 1, channels] per slot")
         out = torch.empty((rows, ch), dtype=x.dtype, device=x.device)

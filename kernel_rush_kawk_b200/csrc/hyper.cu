@@ -16,7 +16,10 @@ namespace {
 
 constexpr int MAX_STREAMS = 8;
 
-template <typename T>
+template <typename T, int V> struct alignas(V * sizeof(T)) Run { T v[V]; };
+
+// V: elements a thread takes at a time (4 where C is a multiple of 4: 16-byte pieces of the streams)
+template <typename T, int V>
 __global__ void hyper_rmsnorm_kernel(T* __restrict__ out, float* x_new, const float* x, const T* __restrict__ branch,
                                      const float* __restrict__ fold, const float* __restrict__ read,
                                      const float* __restrict__ gain, float offset, int S, int C, float eps) {
@@ -33,37 +36,54 @@ __global__ void hyper_rmsnorm_kernel(T* __restrict__ out, float* x_new, const fl
   grid_dependency_wait();
   const size_t base = (size_t)blockIdx.x * S * C;
   float sq = 0.f;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float xs[MAX_STREAMS];
+  for (int c = V * threadIdx.x; c < C; c += V * blockDim.x) {
+    Run<float, V> xs[MAX_STREAMS];
 #pragma unroll
     for (int s = 0; s < MAX_STREAMS; ++s)
-      if (s < S) xs[s] = x[base + (size_t)s * C + c];
-    float u = 0.f;
+      if (s < S) xs[s] = *reinterpret_cast<const Run<float, V>*>(x + base + (size_t)s * C + c);
+    Run<float, V> u;
+#pragma unroll
+    for (int k = 0; k < V; ++k) u.v[k] = 0.f;
     if (branch) {
-      const float y = to_float<T>(branch[(size_t)blockIdx.x * C + c]);
+      const Run<T, V> y = *reinterpret_cast<const Run<T, V>*>(branch + (size_t)blockIdx.x * C + c);
 #pragma unroll
       for (int t = 0; t < MAX_STREAMS; ++t) {
         if (t < S) {
-          float v = 0.f;
+          Run<float, V> v;
 #pragma unroll
-          for (int s = 0; s < MAX_STREAMS; ++s)
-            if (s < S) v += M[s * S + t] * xs[s];
-          v += b[t] * y;
-          x_new[base + (size_t)t * C + c] = v;
-          u += a[t] * v;
+          for (int k = 0; k < V; ++k) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+              if (s < S) acc += M[s * S + t] * xs[s].v[k];
+            acc += b[t] * to_float<T>(y.v[k]);
+            v.v[k] = acc;
+            u.v[k] += a[t] * acc;
+          }
+          *reinterpret_cast<Run<float, V>*>(x_new + base + (size_t)t * C + c) = v;
         }
       }
     } else {
 #pragma unroll
       for (int s = 0; s < MAX_STREAMS; ++s)
-        if (s < S) u += a[s] * xs[s];
+        if (s < S) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) u.v[k] += a[s] * xs[s].v[k];
+        }
     }
-    u_s[c] = u;
-    sq += u * u;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      u_s[c + k] = u.v[k];
+      sq += u.v[k] * u.v[k];
+    }
   }
   const float rstd = rsqrtf(block_sum(sq, scratch) / (float)C + eps);
-  for (int c = threadIdx.x; c < C; c += blockDim.x)
-    out[(size_t)blockIdx.x * C + c] = from_float<T>(u_s[c] * rstd * (offset + gain[c]));
+  for (int c = V * threadIdx.x; c < C; c += V * blockDim.x) {
+    Run<T, V> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = from_float<T>(u_s[c + k] * rstd * (offset + gain[c + k]));
+    *reinterpret_cast<Run<T, V>*>(out + (size_t)blockIdx.x * C + c) = o;
+  }
 }
 
 // one block per row; columns q0 .. k0 are the q row, k0 .. v0 the k row, v0 .. end the v row
@@ -107,16 +127,17 @@ KRK_API int krk_hyper_rmsnorm(void* out, float* x_new, const float* x, const voi
   const size_t smem = (size_t)C * sizeof(float);
   if (smem > 200 * 1024) return -2;
   const int threads = C >= 4096 ? 512 : (C >= 1024 ? 256 : 128);
+  const bool vec = C % 4 == 0;  // rows of the streams, the pending output and the result then start on 16 (8) bytes
   if (dtype == KRK_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(hyper_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return (int)launch_pdl(hyper_rmsnorm_kernel<float>, dim3(rows), dim3(threads), smem, stream, (float*)out, x_new, x,
-                           (const float*)branch, fold, read, gain, offset, S, C, eps);
+    auto kern = vec ? hyper_rmsnorm_kernel<float, 4> : hyper_rmsnorm_kernel<float, 1>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (float*)out, x_new, x, (const float*)branch, fold,
+                           read, gain, offset, S, C, eps);
   }
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(hyper_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return (int)launch_pdl(hyper_rmsnorm_kernel<bf16>, dim3(rows), dim3(threads), smem, stream, (bf16*)out, x_new, x,
-                         (const bf16*)branch, fold, read, gain, offset, S, C, eps);
+  auto kern = vec ? hyper_rmsnorm_kernel<bf16, 4> : hyper_rmsnorm_kernel<bf16, 1>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (bf16*)out, x_new, x, (const bf16*)branch, fold,
+                         read, gain, offset, S, C, eps);
 }
 
 KRK_API int krk_bias_row_norm(void* proj, int stride, int q0, int k0, int v0, int end, const float* bias,

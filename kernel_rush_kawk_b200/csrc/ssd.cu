@@ -1,7 +1,7 @@
 // A state-space mixer with a matrix state per head and a scalar decay per head and token (Mamba-2).
 //
-// krk_causal_conv_silu: y[r, c] = silu(b[c] + sum_j w[c, j] * in[r - (taps - 1 - j), c]) over the rows of one
-// sequence; rows before the step's first come from the sequence's stored tail (its last taps - 1 inputs),
+// krk_causal_conv_silu: y[r, c] = silu(b[c] + sum_j w[j, c] * in[r - (taps - 1 - j), c]) over the rows of one
+// sequence (the weights come tap-major, [taps, channels], so that a thread's channels lie side by side); rows before the step's first come from the sequence's stored tail (its last taps - 1 inputs),
 // rows before the sequence's start are zero (the tail of a fresh slot is zero). krk_conv_tail_update then
 // stores the new last taps - 1 inputs; it is a launch of its own because rows of the step still read the
 // old tail while the step's last rows would overwrite it.
@@ -9,9 +9,9 @@
 // krk_ssd_scan: per (sequence, head), with S [N, P] float32 carried from token to token,
 //   dt = softplus(dt_raw + dt_bias_h);  a = exp(-exp(A_log_h) * dt)
 //   S <- a S + dt B x^T;  y = S^T C + D_h x
-// A block holds one head's state in registers: column p of S is spread over NS lanes of one warp, which hold
-// the rows n = ns, ns + NS, ...; a token's y_p is each lane's ordered partial sum followed by a fixed
-// exchange between the NS lanes. Tokens are staged through shared memory sixteen at a time (x, B, C as
+// A block holds one head's state in registers: column p of S is spread over NS lanes of one warp, each holding
+// a run of consecutive rows; a token's y_p is each lane's partial sum (four ordered sums, added) followed by a
+// fixed exchange between the NS lanes. Tokens are staged through shared memory sixteen at a time (x, B, C as
 // float32, dt and a computed once per token). Steps of one sequence's many tokens run in three passes so that
 // all SMs work on one sequence: every chunk of `chunk` tokens scans from a zero state to its local end state
 // (pass 1), one small kernel walks a sequence's chunks in order, S_in[c+1] = (prod a) S_in[c] + local[c], and
@@ -30,7 +30,22 @@ constexpr int MAX_TAPS = 16;  // the convolution's taps
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-template <typename T>
+// V consecutive elements as floats, in one access of V * sizeof(T) bytes (the address is aligned to that)
+template <typename T, int V> struct alignas(V * sizeof(T)) Run { T v[V]; };
+template <typename T, int V> __device__ __forceinline__ void load_run(const T* p, float* f) {
+  const Run<T, V> raw = *reinterpret_cast<const Run<T, V>*>(p);
+#pragma unroll
+  for (int i = 0; i < V; ++i) f[i] = to_float<T>(raw.v[i]);
+}
+template <typename T, int V> __device__ __forceinline__ void store_run(T* p, const float* f) {
+  Run<T, V> raw;
+#pragma unroll
+  for (int i = 0; i < V; ++i) raw.v[i] = from_float<T>(f[i]);
+  *reinterpret_cast<Run<T, V>*>(p) = raw;
+}
+
+// a thread takes V consecutive channels of one row (V = 1, or 16 bytes' worth where sizes and addresses allow)
+template <typename T, int V>
 __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict__ in, int in_stride,
                                         const float* __restrict__ w, const float* __restrict__ bias,
                                         const T* __restrict__ tail, int taps, int ch, const int* __restrict__ row_seq,
@@ -42,16 +57,21 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
   const int first = cu_q[seq];
   const int keep = taps - 1;
   const T* old = tail + (size_t)seq_slot[seq] * max(keep, 1) * ch;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ch; c += gridDim.y * blockDim.x) {
-    float acc = bias[c];
+  for (int c = V * (blockIdx.y * blockDim.x + threadIdx.x); c < ch; c += V * gridDim.y * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = bias[c + i];
     for (int j = 0; j < taps; ++j) {
-      const int src = r - (keep - j);  // the row that column j multiplies
-      float v;
-      if (src >= first) v = to_float<T>(in[(size_t)src * in_stride + c]);
-      else v = to_float<T>(old[(size_t)(keep - (first - src)) * ch + c]);  // first - src in 1..keep
-      acc += w[(size_t)c * taps + j] * v;
+      const int src = r - (keep - j);  // the row that tap j multiplies
+      float v[V];
+      if (src >= first) load_run<T, V>(in + (size_t)src * in_stride + c, v);
+      else load_run<T, V>(old + (size_t)(keep - (first - src)) * ch + c, v);  // first - src in 1..keep
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] += w[(size_t)j * ch + c + i] * v[i];
     }
-    out[(size_t)r * ch + c] = from_float<T>(silu_f(acc));
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = silu_f(acc[i]);
+    store_run<T, V>(out + (size_t)r * ch + c, acc);
   }
 }
 
@@ -98,54 +118,61 @@ struct SsdArgs {
 
 // MODE 0: the whole step of a sequence, from and to the stored state. MODE 1: a chunk from zero to its local
 // end state (no y). MODE 3: a chunk from its starting state, y only.
+// Lane layout: a warp covers PW = 32 / NS columns; lane = ns * PW + (p % PW), so that the lanes of one quarter of
+// a warp read one 16-byte piece of B (or C) together and the lanes of one ns read consecutive columns of the state.
+// Lane ns holds the state's rows n0 .. n0 + NPT - 1, n0 = ns * NPT; B and C are staged with their rows padded
+// with zeros up to NS * NPT, so that the token loop has no bounds to check (a row beyond N stays zero).
 template <typename T, int NPT, int MODE>
 __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
   extern __shared__ __align__(16) float smem[];
   grid_launch_dependents();
-  grid_dependency_wait();
   const int h = blockIdx.x, seq = blockIdx.y, chunk = MODE == 0 ? 0 : blockIdx.z;
   const int P = a.P, N = a.N, H = a.H;
+  const int NP = NS * NPT;  // padded rows of B and C in shared memory
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int PW = 32 / NS;
+  const int ns = lane / PW, p = warp * PW + lane % PW;
+  const int n0 = ns * NPT;
+  const bool live = p < P;
+
+  float* xs = smem;                 // [TOK][P]
+  float* Bs = xs + TOK * P;         // [TOK][NP]
+  float* Cs = Bs + TOK * NP;        // [TOK][NP]
+  float* dts = Cs + TOK * NP;       // [TOK]
+  float* as = dts + TOK;            // [TOK]
+  float* ys = as + TOK;             // [TOK][P]
+  for (int i = threadIdx.x; i < 2 * TOK * NP; i += blockDim.x) Bs[i] = 0.f;  // the padding stays zero
+  const float bias = a.dt_bias[h], rate = expf(a.a_log[h]), skip = a.skip[h];  // weights: no kernel writes them
+
+  grid_dependency_wait();
   const int qlen = a.seq_qlen[seq];
   const int t_lo = MODE == 0 ? 0 : chunk * a.chunk;
   if (t_lo >= qlen) return;
   const int t_hi = MODE == 0 ? qlen : min(qlen, t_lo + a.chunk);
   const int row0 = a.cu_q[seq];
   const int g = h / (H / a.G);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int PW = 32 / NS;
-  const int ns = lane / PW, p = warp * PW + lane % PW;
-  const bool live = p < P;
-
-  float* xs = smem;                 // [TOK][P]
-  float* Bs = xs + TOK * P;         // [TOK][N]
-  float* Cs = Bs + TOK * N;         // [TOK][N]
-  float* dts = Cs + TOK * N;        // [TOK]
-  float* as = dts + TOK;            // [TOK]
-  float* ys = as + TOK;             // [TOK][P]
 
   float s[NPT];
   float* st = nullptr;
   if (MODE == 0) st = a.state + ((size_t)a.seq_slot[seq] * H + h) * N * P;
   if (MODE == 3) st = a.chunk_state + (((size_t)seq * a.max_chunks + chunk) * H + h) * N * P;
 #pragma unroll
-  for (int j = 0; j < NPT; ++j) {
-    const int n = ns + j * NS;
-    s[j] = (MODE != 1 && live && n < N) ? st[(size_t)n * P + p] : 0.f;
-  }
-  const float bias = a.dt_bias[h], rate = expf(a.a_log[h]), skip = a.skip[h];
+  for (int j = 0; j < NPT; ++j) s[j] = (MODE != 1 && live && n0 + j < N) ? st[(size_t)(n0 + j) * P + p] : 0.f;
   float decay_prod = 1.f;
 
   for (int t0 = t_lo; t0 < t_hi; t0 += TOK) {
     const int nt = min(TOK, t_hi - t0);
-    __syncthreads();  // the tile before is consumed (and its y stored)
-    for (int i = threadIdx.x; i < nt * P; i += blockDim.x) {
-      const int t = i / P, c = i % P;
-      xs[t * P + c] = to_float<T>(((const T*)a.x)[(size_t)(row0 + t0 + t) * a.x_stride + h * P + c]);
-    }
-    for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
-      const int t = i / N, c = i % N;
-      Bs[t * N + c] = to_float<T>(((const T*)a.B)[(size_t)(row0 + t0 + t) * a.b_stride + g * N + c]);
-      if (MODE != 1) Cs[t * N + c] = to_float<T>(((const T*)a.C)[(size_t)(row0 + t0 + t) * a.c_stride + g * N + c]);
+    __syncthreads();  // the tile before is consumed (and its y stored); the first time: the padding is written
+    for (int t = warp; t < nt; t += n_warps) {
+      const size_t r = (size_t)(row0 + t0 + t);
+      const T* xr = (const T*)a.x + r * a.x_stride + h * P;
+      for (int c = lane; c < P; c += 32) xs[t * P + c] = to_float<T>(xr[c]);
+      const T* br = (const T*)a.B + r * a.b_stride + g * N;
+      for (int c = lane; c < N; c += 32) Bs[t * NP + c] = to_float<T>(br[c]);
+      if (MODE != 1) {
+        const T* cr = (const T*)a.C + r * a.c_stride + g * N;
+        for (int c = lane; c < N; c += 32) Cs[t * NP + c] = to_float<T>(cr[c]);
+      }
     }
     if (threadIdx.x < nt) {
       const float d = softplus_f(to_float<T>(((const T*)a.dt)[(size_t)(row0 + t0 + threadIdx.x) * a.dt_stride + h]) + bias);
@@ -157,18 +184,26 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
       const float at = as[t];
       const float xv = live ? xs[t * P + p] : 0.f;
       const float dx = dts[t] * xv;
-      const float* Bt = Bs + t * N;
-      const float* Ct = Cs + t * N;
-      float acc = 0.f;
+      const float4* Bt = reinterpret_cast<const float4*>(Bs + t * NP + n0);
+      const float4* Ct = reinterpret_cast<const float4*>(Cs + t * NP + n0);
+      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
-      for (int j = 0; j < NPT; ++j) {
-        const int n = ns + j * NS;
-        if (n < N) {
-          s[j] = at * s[j] + Bt[n] * dx;
-          if (MODE != 1) acc += s[j] * Ct[n];
+      for (int j = 0; j < NPT / 4; ++j) {
+        const float4 b = Bt[j];
+        s[4 * j] = fmaf(at, s[4 * j], b.x * dx);
+        s[4 * j + 1] = fmaf(at, s[4 * j + 1], b.y * dx);
+        s[4 * j + 2] = fmaf(at, s[4 * j + 2], b.z * dx);
+        s[4 * j + 3] = fmaf(at, s[4 * j + 3], b.w * dx);
+        if (MODE != 1) {
+          const float4 c = Ct[j];
+          acc0 = fmaf(s[4 * j], c.x, acc0);
+          acc1 = fmaf(s[4 * j + 1], c.y, acc1);
+          acc2 = fmaf(s[4 * j + 2], c.z, acc2);
+          acc3 = fmaf(s[4 * j + 3], c.w, acc3);
         }
       }
       if (MODE != 1) {
+        float acc = (acc0 + acc1) + (acc2 + acc3);
         for (int o = PW; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (ns == 0 && live) ys[t * P + p] = acc + skip * xv;
       }
@@ -176,24 +211,23 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
     }
     if (MODE != 1) {
       __syncthreads();
-      for (int i = threadIdx.x; i < nt * P; i += blockDim.x) {
-        const int t = i / P, c = i % P;
-        a.y[(size_t)(row0 + t0 + t) * H * P + h * P + c] = ys[t * P + c];
+      for (int t = warp; t < nt; t += n_warps) {
+        float* yr = a.y + (size_t)(row0 + t0 + t) * H * P + h * P;
+        for (int c = lane; c < P; c += 32) yr[c] = ys[t * P + c];
       }
     }
   }
   if (MODE == 3) return;
   float* dst = MODE == 0 ? st : a.chunk_state + (((size_t)seq * a.max_chunks + chunk) * H + h) * N * P;
 #pragma unroll
-  for (int j = 0; j < NPT; ++j) {
-    const int n = ns + j * NS;
-    if (live && n < N) dst[(size_t)n * P + p] = s[j];
-  }
+  for (int j = 0; j < NPT; ++j)
+    if (live && n0 + j < N) dst[(size_t)(n0 + j) * P + p] = s[j];
   if (MODE == 1 && threadIdx.x == 0) a.chunk_decay[((size_t)seq * a.max_chunks + chunk) * H + h] = decay_prod;
 }
 
 // pass 2: a sequence's chunks in order. chunk_state[c] holds chunk c's local end state and receives its
-// starting state; the stored state receives the sequence's final one.
+// starting state; the stored state receives the sequence's final one. The chunks' values are fetched eight at a
+// time before the walk, which itself is a chain of dependent sums.
 __global__ void ssd_combine_kernel(SsdArgs a) {
   grid_launch_dependents();
   grid_dependency_wait();
@@ -203,20 +237,31 @@ __global__ void ssd_combine_kernel(SsdArgs a) {
   const int n_chunks = (qlen + a.chunk - 1) / a.chunk;
   const size_t NP = (size_t)a.N * a.P;
   float* st = a.state + ((size_t)a.seq_slot[seq] * a.H + h) * NP;
+  const size_t step = (size_t)a.H * NP;  // from one chunk's state to the next one's
   for (size_t e = blockIdx.z * blockDim.x + threadIdx.x; e < NP; e += (size_t)gridDim.z * blockDim.x) {
     float run = st[e];
-    for (int c = 0; c < n_chunks; ++c) {
-      const size_t at = ((size_t)seq * a.max_chunks + c) * a.H + h;
-      float* cs = a.chunk_state + at * NP + e;
-      const float local = *cs;
-      *cs = run;
-      run = a.chunk_decay[at] * run + local;
+    float* cs = a.chunk_state + ((size_t)seq * a.max_chunks * a.H + h) * NP + e;
+    const float* cd = a.chunk_decay + (size_t)seq * a.max_chunks * a.H + h;
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {
+      float local[8], decay[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + i < n_chunks) {
+          local[i] = __ldcg(cs + (size_t)(c0 + i) * step);
+          decay[i] = cd[(size_t)(c0 + i) * a.H];
+        }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + i < n_chunks) {
+          cs[(size_t)(c0 + i) * step] = run;
+          run = fmaf(decay[i], run, local[i]);
+        }
     }
     st[e] = run;
   }
 }
 
-template <typename T>
+template <typename T, int V>
 __global__ void gated_group_norm_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
                                         const float* __restrict__ y, const T* __restrict__ z, int z_stride,
                                         const float* __restrict__ weight, int inner, int parts, float eps) {
@@ -227,14 +272,24 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, int out_stride, int
   const int r = blockIdx.x, part = blockIdx.y;
   const int n = inner / parts, c0 = part * n;
   float sq = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = y[(size_t)r * inner + c0 + i] * silu_f(to_float<T>(z[(size_t)r * z_stride + c0 + i]));
-    row_s[i] = v;
-    sq += v * v;
+  for (int i = V * threadIdx.x; i < n; i += V * blockDim.x) {
+    float yv[V], zv[V];
+    load_run<float, V>(y + (size_t)r * inner + c0 + i, yv);
+    load_run<T, V>(z + (size_t)r * z_stride + c0 + i, zv);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float v = yv[k] * silu_f(zv[k]);
+      row_s[i + k] = v;
+      sq += v * v;
+    }
   }
   const float rstd = rsqrtf(block_sum(sq, scratch) / (float)n + eps);
-  for (int i = threadIdx.x; i < n; i += blockDim.x)
-    out[(size_t)r * out_stride + out_col + c0 + i] = from_float<T>(row_s[i] * rstd * weight[c0 + i] * out_scale);
+  for (int i = V * threadIdx.x; i < n; i += V * blockDim.x) {
+    float o[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) o[k] = row_s[i + k] * rstd * weight[c0 + i + k] * out_scale;
+    store_run<T, V>(out + (size_t)r * out_stride + out_col + c0 + i, o);
+  }
 }
 
 template <typename T, int MODE>
@@ -264,10 +319,11 @@ int run_scan(SsdArgs a, int n_seqs, int max_q_len, cudaStream_t stream) {
   const int PW = 32 / NS;
   const int warps = (P + PW - 1) / PW;
   if (warps > 32) return -2;
-  const int npt = (N + NS - 1) / NS;
+  int npt = (N + NS - 1) / NS;
   if (npt > 64) return -2;
+  npt = npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;  // the kernels' instantiations
   const int threads = warps * 32;
-  const size_t smem = (size_t)(TOK * (2 * P + 2 * N) + 2 * TOK) * sizeof(float);
+  const size_t smem = (size_t)(TOK * (2 * P + 2 * NS * npt) + 2 * TOK) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   if (a.chunk_state && a.chunk > 0 && max_q_len > a.chunk) {
     a.max_chunks = (max_q_len + a.chunk - 1) / a.chunk;
@@ -275,7 +331,7 @@ int run_scan(SsdArgs a, int n_seqs, int max_q_len, cudaStream_t stream) {
     int rc = launch_scan<T, 1>(a, NS, npt, grid, threads, smem, stream);
     if (rc) return rc;
     const int NP = N * P;
-    rc = (int)launch_pdl(ssd_combine_kernel, dim3(a.H, n_seqs, (NP + 1023) / 1024), dim3(256), 0, stream, a);
+    rc = (int)launch_pdl(ssd_combine_kernel, dim3(a.H, n_seqs, (NP + 255) / 256), dim3(256), 0, stream, a);
     if (rc) return rc;
     return launch_scan<T, 3>(a, NS, npt, grid, threads, smem, stream);
   }
@@ -291,13 +347,19 @@ KRK_API int krk_causal_conv_silu(void* out, const void* in, int in_stride, const
   if (taps < 1 || taps > MAX_TAPS) return -2;
   const int threads = 256;
   const int cols = min(64, (ch + threads - 1) / threads);
+  const int V = dtype == KRK_DTYPE_F32 ? 4 : 8;
+  const bool vec = ch % V == 0 && in_stride % V == 0 && (((uintptr_t)in | (uintptr_t)out | (uintptr_t)tail) & 15) == 0;
+  const int vcols = min(64, (ch / V + threads - 1) / threads);
   int rc;
-  if (dtype == KRK_DTYPE_F32)
-    rc = (int)launch_pdl(causal_conv_silu_kernel<float>, dim3(rows, cols), dim3(threads), 0, stream, (float*)out,
-                         (const float*)in, in_stride, w, bias, (const float*)tail, taps, ch, row_seq, cu_q, seq_slot);
-  else
-    rc = (int)launch_pdl(causal_conv_silu_kernel<bf16>, dim3(rows, cols), dim3(threads), 0, stream, (bf16*)out,
-                         (const bf16*)in, in_stride, w, bias, (const bf16*)tail, taps, ch, row_seq, cu_q, seq_slot);
+  if (dtype == KRK_DTYPE_F32) {
+    auto kern = vec ? causal_conv_silu_kernel<float, 4> : causal_conv_silu_kernel<float, 1>;
+    rc = (int)launch_pdl(kern, dim3(rows, vec ? vcols : cols), dim3(threads), 0, stream, (float*)out, (const float*)in,
+                         in_stride, w, bias, (const float*)tail, taps, ch, row_seq, cu_q, seq_slot);
+  } else {
+    auto kern = vec ? causal_conv_silu_kernel<bf16, 8> : causal_conv_silu_kernel<bf16, 1>;
+    rc = (int)launch_pdl(kern, dim3(rows, vec ? vcols : cols), dim3(threads), 0, stream, (bf16*)out, (const bf16*)in,
+                         in_stride, w, bias, (const bf16*)tail, taps, ch, row_seq, cu_q, seq_slot);
+  }
   if (rc || taps == 1) return rc;
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(conv_tail_update_kernel<float>, dim3(n_seqs, cols), dim3(threads), 0, stream, (float*)tail,
@@ -332,14 +394,18 @@ KRK_API int krk_gated_group_norm(void* out, int out_stride, int out_col, float o
   const size_t smem = (size_t)n * sizeof(float);
   if (smem > 200 * 1024) return -2;
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  // four elements a thread (16 bytes of y, 8 or 16 of the gate and the result) where sizes and addresses allow
+  const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
+  const bool vec = n % 4 == 0 && z_stride % 4 == 0 && out_stride % 4 == 0 && out_col % 4 == 0 &&
+                   ((uintptr_t)y & 15) == 0 && (((uintptr_t)z | (uintptr_t)out) & (4 * esz - 1)) == 0;
   if (dtype == KRK_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(gated_group_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return (int)launch_pdl(gated_group_norm_kernel<float>, dim3(rows, parts), dim3(threads), smem, stream, (float*)out,
-                           out_stride, out_col, out_scale, y, (const float*)z, z_stride, weight, inner, parts, eps);
+    auto kern = vec ? gated_group_norm_kernel<float, 4> : gated_group_norm_kernel<float, 1>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(kern, dim3(rows, parts), dim3(threads), smem, stream, (float*)out, out_stride, out_col,
+                           out_scale, y, (const float*)z, z_stride, weight, inner, parts, eps);
   }
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(gated_group_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return (int)launch_pdl(gated_group_norm_kernel<bf16>, dim3(rows, parts), dim3(threads), smem, stream, (bf16*)out,
-                         out_stride, out_col, out_scale, y, (const bf16*)z, z_stride, weight, inner, parts, eps);
+  auto kern = vec ? gated_group_norm_kernel<bf16, 4> : gated_group_norm_kernel<bf16, 1>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(kern, dim3(rows, parts), dim3(threads), smem, stream, (bf16*)out, out_stride, out_col, out_scale,
+                         y, (const bf16*)z, z_stride, weight, inner, parts, eps);
 }

@@ -61,7 +61,7 @@ class Mamba2(Branch):
     def bind(self, tensors, runtime):
         self.w = {"in": tensors["in"], "o": tensors["o"]}
         f = lambda key: tensors[key].float().contiguous()
-        self.conv_w, self.conv_b = f("conv"), f("conv.b")
+        self.conv_w, self.conv_b = f("conv").t().contiguous(), f("conv.b")  # tap-major [taps, channels] for the kernel
         self.dt_bias, self.a_log, self.skip, self.norm_w = f("dt_bias"), f("A_log"), f("D"), f("norm")
         self.bind_standalone()
 

@@ -265,14 +265,14 @@ class _WideOps:
 
     def causal_conv_silu(self, x, w, b, tail, batch):
         rows, ch = x.shape
-        taps = w.shape[1]
+        taps = w.shape[0]  # tap-major weights [taps, channels]
         out = torch.empty((rows, ch), dtype=torch.float32)
         row0 = 0
         for slot, n in zip(batch.slots, batch.q_lens):
             seq = torch.cat([tail[slot][-(taps - 1):].float(), x[row0:row0 + n].float()]) if taps > 1 else x[row0:row0 + n].float()
             acc = b.float()[None, :].repeat(n, 1)
             for j in range(taps):
-                acc += seq[j:j + n] * w[:, j].float()
+                acc += seq[j:j + n] * w[j].float()
             out[row0:row0 + n] = acc
             if taps > 1:
                 tail[slot][-(taps - 1):] = seq[n:].to(tail.dtype)
