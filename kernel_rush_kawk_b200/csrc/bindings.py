@@ -274,7 +274,7 @@ class Kernels:
                  "tcgen05 gemm")
         return out
 
-    def _skinny(self, x, w, out_dtype, swiglu_rows=0, gate_act=1):
+    def _skinny(self, x, w, out_dtype, swiglu_rows=0, gate_act=1, act_limit=0.0):
         """x: a tensor or a Normed not yet computed (then the add and the norm run in
         the kernel's prologue)."""
         lazy = not isinstance(x, torch.Tensor)
@@ -287,7 +287,7 @@ class Kernels:
         x_new = x.x_new if lazy and x.branch is not None else None
         self._ok(self.core.krk_skinny_linear(
             out.data_ptr(), src.data_ptr(), w.data_ptr(), _ptr(branch), _ptr(gain), _ptr(x_new),
-            int(gain is not None and gain.dtype == torch.float32), None, M, N, K, float(x.eps) if lazy else 0.0,
+            int(gain is not None and gain.dtype == torch.float32), None, M, N, K, float(x.eps) if lazy else float(act_limit),
             int(gate_act if swiglu_rows > 0 else 0), _code(out_dtype), self._stream()), "skinny product")
         if lazy:
             x.mark_fused()
@@ -682,6 +682,10 @@ class Kernels:
     def gate_up_act(self, h, w_gate_up, intermediate, activation, act_params=None):
         """act(gate h) * (up h) with W = cat(gate, up); silu on few bfloat16 rows runs in the product's epilogue."""
         if act_params is not None:
+            if activation == "swish_clamped" and act_params[1] == 1.702 and self._use_skinny(h, w_gate_up):
+                # few rows: in the product's epilogue (its clamped swish has the slope 1.702 built in)
+                return self._skinny(self._resolve(h), w_gate_up, w_gate_up.dtype, swiglu_rows=intermediate, gate_act=3,
+                                    act_limit=act_params[0])
             return self.gated_act(self.linear(h, w_gate_up), intermediate, activation, act_params=act_params)
         if activation == "silu" and self._use_skinny(h, w_gate_up):
             return self.gate_up_swiglu(h, w_gate_up, intermediate)

@@ -305,6 +305,9 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
     if (m < M && n < N) {
       if (SWIGLU == 2) {  // tanh form of GELU on the gate, gate and up as accumulated (float32), rounded once
         v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) * v2;
+      } else if (SWIGLU == 3) {  // clamped inputs, g' sigmoid(1.702 g') (u' + 1); no norm with it: eps carries the limit
+        const float gate = fminf(v, eps), up = fminf(fmaxf(v2, -eps), eps);
+        v = gate / (1.0f + expf(-1.702f * gate)) * (up + 1.0f);
       } else if (SWIGLU) {
         const float gate = round_to<bf16>(v), up = round_to<bf16>(v2);
         v = round_to<bf16>(gate / (1.0f + expf(-gate))) * up;
@@ -437,6 +440,10 @@ KRK_API int krk_skinny_linear(void* out, const void* x, const void* W, const voi
   if (swiglu == 2) {  // gate and up with the tanh form of GELU; no norm prologue with it
     if (out_dtype != KRK_DTYPE_BF16 || norm) return -4;
     return pick_nt<2, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  }
+  if (swiglu == 3) {  // gate and up clamped at `eps` (the limit), swish with slope 1.702 times (up + 1); no norm prologue
+    if (out_dtype != KRK_DTYPE_BF16 || norm) return -4;
+    return pick_nt<3, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
   }
   if (swiglu) {
     if (out_dtype != KRK_DTYPE_BF16) return -4;

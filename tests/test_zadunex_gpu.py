@@ -288,12 +288,14 @@ def test_one_far_key_among_hundreds_is_found(dtype, loud, T):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows, inter, limit", [(5, 24, 1.0), (40, 33, 0.6), (3, 64, 7.0)])
-def test_dense_feed_forward_with_clamped_inputs(dtype, rows, inter, limit):
+@pytest.mark.parametrize("rows, inter, limit, C", [(5, 24, 1.0, 48), (40, 33, 0.6, 48), (3, 64, 7.0, 48),
+                                                   (5, 40, 1.0, 64), (13, 96, 0.8, 128), (1, 33, 0.5, 96)])
+def test_dense_feed_forward_with_clamped_inputs(dtype, rows, inter, limit, C):
+    """Widths that are a multiple of 32 take, for few bfloat16 rows, the product whose epilogue clamps and
+    multiplies; the others the product and the activation kernel."""
     from kernel_rush_kawk_b200.parts import GatedMLP
 
     rt = runtime(dtype)
-    C = 48
     part = GatedMLP({"hidden": C, "intermediate": inter, "activation": "swish_clamped", "limit": limit, "slope": 1.702})
     w = {"gate": rand((inter, C), 1, 0.4), "up": rand((inter, C), 2, 0.4), "down": rand((C, inter), 3, 0.3)}
     dev, ref = as_path(w, dtype)
