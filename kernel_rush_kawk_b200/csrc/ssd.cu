@@ -58,16 +58,19 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
   const int keep = taps - 1;
   const T* old = tail + (size_t)seq_slot[seq] * max(keep, 1) * ch;
   for (int c = V * (blockIdx.y * blockDim.x + threadIdx.x); c < ch; c += V * gridDim.y * blockDim.x) {
+    constexpr int W = V >= 4 ? 4 : 1;  // the weights' floats in 16-byte pieces where the channels are (V = 1, 4 or 8)
     float acc[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] = bias[c + i];
+    for (int i = 0; i < V; i += W) load_run<float, W>(bias + c + i, acc + i);
     for (int j = 0; j < taps; ++j) {
       const int src = r - (keep - j);  // the row that tap j multiplies
-      float v[V];
+      float v[V], wj[V];
       if (src >= first) load_run<T, V>(in + (size_t)src * in_stride + c, v);
       else load_run<T, V>(old + (size_t)(keep - (first - src)) * ch + c, v);  // first - src in 1..keep
 #pragma unroll
-      for (int i = 0; i < V; ++i) acc[i] += w[(size_t)j * ch + c + i] * v[i];
+      for (int i = 0; i < V; i += W) load_run<float, W>(w + (size_t)j * ch + c + i, wj + i);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] += wj[i] * v[i];
     }
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = silu_f(acc[i]);
@@ -118,11 +121,18 @@ struct SsdArgs {
 
 // MODE 0: the whole step of a sequence, from and to the stored state. MODE 1: a chunk from zero to its local
 // end state (no y). MODE 3: a chunk from its starting state, y only.
-// Lane layout: a warp covers PW = 32 / NS columns; lane = ns * PW + (p % PW), so that the lanes of one quarter of
-// a warp read one 16-byte piece of B (or C) together and the lanes of one ns read consecutive columns of the state.
-// Lane ns holds the state's rows n0 .. n0 + NPT - 1, n0 = ns * NPT; B and C are staged with their rows padded
-// with zeros up to NS * NPT, so that the token loop has no bounds to check (a row beyond N stays zero).
-template <typename T, int NPT, int MODE>
+// A lane holds NPT consecutive rows of PC consecutive columns of the state. NS lanes of one warp share a group of
+// PC columns (lane ns holds rows n0 .. n0 + NPT - 1, n0 = ns * NPT); a warp covers PW = 32 / NS column groups, and
+// lane = ns * PW + (group % PW), so that the lanes of one ns read one piece of B (or C) together. What a token
+// costs a lane in shared-memory reads is 2 NPT + PC floats for 3 NPT PC multiply-adds, which is why a lane takes
+// several columns where the state is large: the reads, not the arithmetic, bound the one-column form. B and C
+// are staged with their rows padded with zeros up to NS * NPT, so that the token loop has no bounds to check
+// (a row beyond N stays zero). Several columns a lane are taken only where P is a multiple of them, so that a
+// lane's columns are one aligned piece of a row of x and of the state.
+// y of a token: each lane's ordered partial sums over its rows, then over the NS lanes of the group: first
+// log2(PC) exchange steps that halve the columns a lane carries while doubling the lanes summed into them, then
+// plain exchanges; the order is fixed by (N, P) alone.
+template <typename T, int NPT, int PC, int MODE>
 __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
   extern __shared__ __align__(16) float smem[];
   grid_launch_dependents();
@@ -131,9 +141,10 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
   const int NP = NS * NPT;  // padded rows of B and C in shared memory
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const int PW = 32 / NS;
-  const int ns = lane / PW, p = warp * PW + lane % PW;
+  const int ns = lane / PW, p0 = (warp * PW + lane % PW) * PC;
   const int n0 = ns * NPT;
-  const bool live = p < P;
+  constexpr int ACCS = PC == 1 ? 4 : (PC == 2 ? 2 : 1);  // ordered partial sums per column
+  constexpr int LOG_PC = PC == 1 ? 0 : (PC == 2 ? 1 : 2);
 
   float* xs = smem;                 // [TOK][P]
   float* Bs = xs + TOK * P;         // [TOK][NP]
@@ -152,12 +163,20 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
   const int row0 = a.cu_q[seq];
   const int g = h / (H / a.G);
 
-  float s[NPT];
+  float s[PC][NPT];
   float* st = nullptr;
   if (MODE == 0) st = a.state + ((size_t)a.seq_slot[seq] * H + h) * N * P;
   if (MODE == 3) st = a.chunk_state + (((size_t)seq * a.max_chunks + chunk) * H + h) * N * P;
+  const bool live = p0 < P;  // with several columns a lane, P is a multiple of PC: all of them or none
 #pragma unroll
-  for (int j = 0; j < NPT; ++j) s[j] = (MODE != 1 && live && n0 + j < N) ? st[(size_t)(n0 + j) * P + p] : 0.f;
+  for (int j = 0; j < NPT; ++j) {
+    float row[PC];
+#pragma unroll
+    for (int c = 0; c < PC; ++c) row[c] = 0.f;
+    if (MODE != 1 && live && n0 + j < N) load_run<float, PC>(st + (size_t)(n0 + j) * P + p0, row);
+#pragma unroll
+    for (int c = 0; c < PC; ++c) s[c][j] = row[c];
+  }
   float decay_prod = 1.f;
 
   for (int t0 = t_lo; t0 < t_hi; t0 += TOK) {
@@ -181,31 +200,61 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
-      const float at = as[t];
-      const float xv = live ? xs[t * P + p] : 0.f;
-      const float dx = dts[t] * xv;
+      const float at = as[t], dtt = dts[t];
+      float xv[PC], dx[PC], acc[PC][ACCS];
+#pragma unroll
+      for (int c = 0; c < PC; ++c) xv[c] = 0.f;
+      if (live) load_run<float, PC>(xs + t * P + p0, xv);
+#pragma unroll
+      for (int c = 0; c < PC; ++c) {
+        dx[c] = dtt * xv[c];
+#pragma unroll
+        for (int i = 0; i < ACCS; ++i) acc[c][i] = 0.f;
+      }
       const float4* Bt = reinterpret_cast<const float4*>(Bs + t * NP + n0);
       const float4* Ct = reinterpret_cast<const float4*>(Cs + t * NP + n0);
-      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
       for (int j = 0; j < NPT / 4; ++j) {
-        const float4 b = Bt[j];
-        s[4 * j] = fmaf(at, s[4 * j], b.x * dx);
-        s[4 * j + 1] = fmaf(at, s[4 * j + 1], b.y * dx);
-        s[4 * j + 2] = fmaf(at, s[4 * j + 2], b.z * dx);
-        s[4 * j + 3] = fmaf(at, s[4 * j + 3], b.w * dx);
+        const float4 b4 = Bt[j];
+        const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+        float cv[4] = {0.f, 0.f, 0.f, 0.f};
         if (MODE != 1) {
-          const float4 c = Ct[j];
-          acc0 = fmaf(s[4 * j], c.x, acc0);
-          acc1 = fmaf(s[4 * j + 1], c.y, acc1);
-          acc2 = fmaf(s[4 * j + 2], c.z, acc2);
-          acc3 = fmaf(s[4 * j + 3], c.w, acc3);
+          const float4 c4 = Ct[j];
+          cv[0] = c4.x; cv[1] = c4.y; cv[2] = c4.z; cv[3] = c4.w;
         }
+#pragma unroll
+        for (int c = 0; c < PC; ++c)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            s[c][4 * j + i] = fmaf(at, s[c][4 * j + i], bv[i] * dx[c]);
+            if (MODE != 1) acc[c][i % ACCS] = fmaf(s[c][4 * j + i], cv[i], acc[c][i % ACCS]);
+          }
       }
       if (MODE != 1) {
-        float acc = (acc0 + acc1) + (acc2 + acc3);
-        for (int o = PW; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (ns == 0 && live) ys[t * P + p] = acc + skip * xv;
+        float v[PC];
+#pragma unroll
+        for (int c = 0; c < PC; ++c)
+          v[c] = ACCS == 4 ? (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]) : (ACCS == 2 ? acc[c][0] + acc[c][1] : acc[c][0]);
+        int col = 0;
+#pragma unroll
+        for (int bit = 0; bit < LOG_PC; ++bit) {  // a lane gives half its columns to the lane that differs in this bit of ns
+          const int half = PC >> (bit + 1);
+          const bool up = (ns >> bit) & 1;
+#pragma unroll
+          for (int i = 0; i < half; ++i) {
+            const float send = up ? v[i] : v[i + half];
+            const float keep = up ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, PW << bit);
+          }
+          col += up ? half : 0;
+        }
+        for (int o = PW * PC; o < 32; o <<= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+        if ((ns >> LOG_PC) == 0 && live) {
+          float xc = xv[0];
+#pragma unroll
+          for (int c = 1; c < PC; ++c) xc = col == c ? xv[c] : xc;
+          ys[t * P + p0 + col] = v[0] + skip * xc;
+        }
       }
       if (MODE == 1) decay_prod *= at;
     }
@@ -220,8 +269,12 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
   if (MODE == 3) return;
   float* dst = MODE == 0 ? st : a.chunk_state + (((size_t)seq * a.max_chunks + chunk) * H + h) * N * P;
 #pragma unroll
-  for (int j = 0; j < NPT; ++j)
-    if (live && n0 + j < N) dst[(size_t)(n0 + j) * P + p] = s[j];
+  for (int j = 0; j < NPT; ++j) {
+    float row[PC];
+#pragma unroll
+    for (int c = 0; c < PC; ++c) row[c] = s[c][j];
+    if (live && n0 + j < N) store_run<float, PC>(dst + (size_t)(n0 + j) * P + p0, row);
+  }
   if (MODE == 1 && threadIdx.x == 0) a.chunk_decay[((size_t)seq * a.max_chunks + chunk) * H + h] = decay_prod;
 }
 
@@ -293,18 +346,20 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, int out_stride, int
 }
 
 template <typename T, int MODE>
-int launch_scan(const SsdArgs& a, int NS, int npt, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
-#define KRK_SSD_CASE(V)                                                                                          \
-  if (npt <= V) {                                                                                                \
-    if (smem > 48 * 1024)                                                                                        \
-      cudaFuncSetAttribute(ssd_scan_kernel<T, V, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    return (int)launch_pdl(ssd_scan_kernel<T, V, MODE>, grid, dim3(threads), smem, stream, a, NS);               \
+int launch_scan(const SsdArgs& a, int NS, int npt, int pc, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+#define KRK_SSD_CASE(V, C)                                                                                          \
+  if (npt == V && pc == C) {                                                                                        \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(ssd_scan_kernel<T, V, C, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    return (int)launch_pdl(ssd_scan_kernel<T, V, C, MODE>, grid, dim3(threads), smem, stream, a, NS);               \
   }
-  KRK_SSD_CASE(4)
-  KRK_SSD_CASE(8)
-  KRK_SSD_CASE(16)
-  KRK_SSD_CASE(32)
-  KRK_SSD_CASE(64)
+  KRK_SSD_CASE(4, 1)
+  KRK_SSD_CASE(8, 1)
+  KRK_SSD_CASE(16, 1)
+  KRK_SSD_CASE(32, 1)
+  KRK_SSD_CASE(64, 1)
+  KRK_SSD_CASE(8, 2)
+  KRK_SSD_CASE(8, 4)
 #undef KRK_SSD_CASE
   return -2;
 }
@@ -316,26 +371,31 @@ int run_scan(SsdArgs a, int n_seqs, int max_q_len, cudaStream_t stream) {
   int NS = 1;
   while (NS < 32 && P * NS < 128) NS <<= 1;
   while (NS < 32 && (N + NS - 1) / NS > 32 && P * NS * 2 <= 1024) NS <<= 1;
-  const int PW = 32 / NS;
-  const int warps = (P + PW - 1) / PW;
-  if (warps > 32) return -2;
   int npt = (N + NS - 1) / NS;
   if (npt > 64) return -2;
   npt = npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;  // the kernels' instantiations
+  // a lane of 16 or 32 rows of one column becomes a lane of 8 rows of 2 or 4 columns (as many state elements
+  // a lane, a half or a quarter of the reads of B and C a multiply-add)
+  int pc = 1;
+  if (npt == 16 && NS * 2 <= 32 && P % 2 == 0) { pc = 2; NS *= 2; npt = 8; }
+  else if (npt == 32 && NS * 4 <= 32 && P % 4 == 0) { pc = 4; NS *= 4; npt = 8; }
+  const int PW = 32 / NS;
+  const int warps = (P + PW * pc - 1) / (PW * pc);
+  if (warps > 32) return -2;
   const int threads = warps * 32;
   const size_t smem = (size_t)(TOK * (2 * P + 2 * NS * npt) + 2 * TOK) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   if (a.chunk_state && a.chunk > 0 && max_q_len > a.chunk) {
     a.max_chunks = (max_q_len + a.chunk - 1) / a.chunk;
     dim3 grid(a.H, n_seqs, a.max_chunks);
-    int rc = launch_scan<T, 1>(a, NS, npt, grid, threads, smem, stream);
+    int rc = launch_scan<T, 1>(a, NS, npt, pc, grid, threads, smem, stream);
     if (rc) return rc;
     const int NP = N * P;
     rc = (int)launch_pdl(ssd_combine_kernel, dim3(a.H, n_seqs, (NP + 255) / 256), dim3(256), 0, stream, a);
     if (rc) return rc;
-    return launch_scan<T, 3>(a, NS, npt, grid, threads, smem, stream);
+    return launch_scan<T, 3>(a, NS, npt, pc, grid, threads, smem, stream);
   }
-  return launch_scan<T, 0>(a, NS, npt, dim3(a.H, n_seqs), threads, smem, stream);
+  return launch_scan<T, 0>(a, NS, npt, pc, dim3(a.H, n_seqs), threads, smem, stream);
 }
 
 }  // namespace
@@ -348,7 +408,8 @@ KRK_API int krk_causal_conv_silu(void* out, const void* in, int in_stride, const
   const int threads = 256;
   const int cols = min(64, (ch + threads - 1) / threads);
   const int V = dtype == KRK_DTYPE_F32 ? 4 : 8;
-  const bool vec = ch % V == 0 && in_stride % V == 0 && (((uintptr_t)in | (uintptr_t)out | (uintptr_t)tail) & 15) == 0;
+  const bool vec = ch % V == 0 && in_stride % V == 0 &&
+                   (((uintptr_t)in | (uintptr_t)out | (uintptr_t)tail | (uintptr_t)w | (uintptr_t)bias) & 15) == 0;
   const int vcols = min(64, (ch / V + threads - 1) / threads);
   int rc;
   if (dtype == KRK_DTYPE_F32) {
