@@ -21,6 +21,7 @@
 // krk_gated_group_norm: v = y * silu(z); each of `parts` equal parts of the row is divided by its root mean
 // square; times a weight and a scale; rounded once to the path's type.
 #include "common.cuh"
+#include "mma.cuh"  // cp.async
 
 namespace {
 
@@ -117,6 +118,7 @@ struct SsdArgs {
   int max_chunks;        // chunks of the longest sequence
   float* chunk_state;    // [n_seqs, max_chunks, H, N, P]
   float* chunk_decay;    // [n_seqs, max_chunks, H]
+  int vec;               // x, B and C rows can be copied in 16-byte pieces (sizes, strides and addresses allow)
 };
 
 // MODE 0: the whole step of a sequence, from and to the stored state. MODE 1: a chunk from zero to its local
@@ -179,26 +181,64 @@ __global__ void ssd_scan_kernel(SsdArgs a, int NS) {
   }
   float decay_prod = 1.f;
 
+  // Where sizes and addresses allow, a tile's x, B and C rows come as asynchronous 16-byte copies into `raw`,
+  // requested while the tile before is computed, and are widened from there into xs, Bs and Cs; a tile's dt
+  // waits in a register of the thread that turns it into a step size and a decay.
+  constexpr int V = 16 / (int)sizeof(T);
+  T* raw = reinterpret_cast<T*>(ys + TOK * P);  // [TOK][P + 2 N]
+  const int per_tok = P + 2 * N;
+  const int ppt = (P + (MODE != 1 ? 2 : 1) * N) / V;  // pieces a token brings
+  const bool vec = a.vec != 0;
+  float dt_raw = 0.f;
+  auto request = [&](int t0, int nt) {
+    if (vec) {
+      for (int i = threadIdx.x; i < nt * ppt; i += blockDim.x) {
+        const int t = i / ppt, e = (i - t * ppt) * V;  // element e of the token's [x | B | C]
+        const size_t r = (size_t)(row0 + t0 + t);
+        const T* src = e < P ? (const T*)a.x + r * a.x_stride + h * P + e
+                             : (e < P + N ? (const T*)a.B + r * a.b_stride + g * N + (e - P)
+                                          : (const T*)a.C + r * a.c_stride + g * N + (e - P - N));
+        cp_async_16(raw + t * per_tok + e, src);
+      }
+      cp_async_commit();
+    }
+    if (threadIdx.x < nt) dt_raw = to_float<T>(((const T*)a.dt)[(size_t)(row0 + t0 + threadIdx.x) * a.dt_stride + h]);
+  };
+  request(t_lo, min(TOK, t_hi - t_lo));
+
   for (int t0 = t_lo; t0 < t_hi; t0 += TOK) {
     const int nt = min(TOK, t_hi - t0);
+    if (vec) cp_async_wait<0>();
     __syncthreads();  // the tile before is consumed (and its y stored); the first time: the padding is written
-    for (int t = warp; t < nt; t += n_warps) {
-      const size_t r = (size_t)(row0 + t0 + t);
-      const T* xr = (const T*)a.x + r * a.x_stride + h * P;
-      for (int c = lane; c < P; c += 32) xs[t * P + c] = to_float<T>(xr[c]);
-      const T* br = (const T*)a.B + r * a.b_stride + g * N;
-      for (int c = lane; c < N; c += 32) Bs[t * NP + c] = to_float<T>(br[c]);
-      if (MODE != 1) {
-        const T* cr = (const T*)a.C + r * a.c_stride + g * N;
-        for (int c = lane; c < N; c += 32) Cs[t * NP + c] = to_float<T>(cr[c]);
+    if (vec) {
+      for (int i = threadIdx.x; i < nt * ppt; i += blockDim.x) {
+        const int t = i / ppt, e = (i - t * ppt) * V;
+        float f[V];
+        load_run<T, V>(raw + t * per_tok + e, f);
+        float* dst = e < P ? xs + t * P + e : (e < P + N ? Bs + t * NP + (e - P) : Cs + t * NP + (e - P - N));
+#pragma unroll
+        for (int k = 0; k < V; k += 4) store_run<float, 4>(dst + k, f + k);
+      }
+    } else {
+      for (int t = warp; t < nt; t += n_warps) {
+        const size_t r = (size_t)(row0 + t0 + t);
+        const T* xr = (const T*)a.x + r * a.x_stride + h * P;
+        for (int c = lane; c < P; c += 32) xs[t * P + c] = to_float<T>(xr[c]);
+        const T* br = (const T*)a.B + r * a.b_stride + g * N;
+        for (int c = lane; c < N; c += 32) Bs[t * NP + c] = to_float<T>(br[c]);
+        if (MODE != 1) {
+          const T* cr = (const T*)a.C + r * a.c_stride + g * N;
+          for (int c = lane; c < N; c += 32) Cs[t * NP + c] = to_float<T>(cr[c]);
+        }
       }
     }
     if (threadIdx.x < nt) {
-      const float d = softplus_f(to_float<T>(((const T*)a.dt)[(size_t)(row0 + t0 + threadIdx.x) * a.dt_stride + h]) + bias);
+      const float d = softplus_f(dt_raw + bias);
       dts[threadIdx.x] = d;
       as[threadIdx.x] = expf(-rate * d);
     }
     __syncthreads();
+    if (t0 + TOK < t_hi) request(t0 + TOK, min(TOK, t_hi - t0 - TOK));  // in flight while this tile is computed
     for (int t = 0; t < nt; ++t) {
       const float at = as[t], dtt = dts[t];
       float xv[PC], dx[PC], acc[PC][ACCS];
@@ -383,7 +423,11 @@ int run_scan(SsdArgs a, int n_seqs, int max_q_len, cudaStream_t stream) {
   const int warps = (P + PW * pc - 1) / (PW * pc);
   if (warps > 32) return -2;
   const int threads = warps * 32;
-  const size_t smem = (size_t)(TOK * (2 * P + 2 * NS * npt) + 2 * TOK) * sizeof(float);
+  constexpr int V = 16 / (int)sizeof(T);
+  a.vec = P % V == 0 && N % V == 0 && a.x_stride % V == 0 && a.b_stride % V == 0 && a.c_stride % V == 0 &&
+          (((uintptr_t)a.x | (uintptr_t)a.B | (uintptr_t)a.C) & 15) == 0;
+  const size_t smem = (size_t)(TOK * (2 * P + 2 * NS * npt) + 2 * TOK) * sizeof(float) +
+                      (a.vec ? (size_t)TOK * (P + 2 * N) * sizeof(T) : 0);
   if (smem > 200 * 1024) return -2;
   if (a.chunk_state && a.chunk > 0 && max_q_len > a.chunk) {
     a.max_chunks = (max_q_len + a.chunk - 1) / a.chunk;
@@ -442,7 +486,7 @@ KRK_API int krk_ssd_scan(float* y, const void* x, int x_stride, const void* B, i
   a.dt_bias = dt_bias; a.a_log = a_log; a.skip = skip; a.y = y; a.state = state;
   a.H = H; a.P = P; a.N = N; a.G = G;
   a.cu_q = cu_q; a.seq_qlen = seq_qlen; a.seq_slot = seq_slot;
-  a.chunk = chunk; a.max_chunks = 0; a.chunk_state = chunk_state; a.chunk_decay = chunk_decay;
+  a.chunk = chunk; a.max_chunks = 0; a.chunk_state = chunk_state; a.chunk_decay = chunk_decay; a.vec = 0;
   return dtype == KRK_DTYPE_F32 ? run_scan<float>(a, n_seqs, max_q_len, stream) : run_scan<bf16>(a, n_seqs, max_q_len, stream);
 }
 
