@@ -86,22 +86,45 @@ __global__ void hyper_rmsnorm_kernel(T* __restrict__ out, float* x_new, const fl
   }
 }
 
-// one block per row; columns q0 .. k0 are the q row, k0 .. v0 the k row, v0 .. end the v row
-template <typename T>
+// one block per row; columns q0 .. k0 are the q row, k0 .. v0 the k row, v0 .. end the v row. A thread takes V
+// consecutive elements at a time (V = 1, or 16 bytes of the row where the three parts' sizes, the row stride and
+// the addresses are multiples of that: a piece then lies in one part).
+template <typename T, int V>
 __global__ void bias_row_norm_kernel(T* proj, int stride, int q0, int k0, int v0, int end,
                                      const float* __restrict__ bias, const float* __restrict__ gain, float eps) {
   extern __shared__ __align__(16) float row_s[];  // end - q0 floats
   __shared__ float scratch[32];
+  constexpr int W = V >= 4 ? 4 : 1;  // the float32 vectors' pieces
   grid_launch_dependents();
   grid_dependency_wait();
   T* row = proj + (size_t)blockIdx.x * stride + q0;
   const int nq = k0 - q0, nk = v0 - k0, n = end - q0;
   float sq_q = 0.f, sq_k = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = to_float<T>(row[i]) + (bias ? bias[i] : 0.f);
-    row_s[i] = v;
-    if (i < nq) sq_q += v * v;
-    else if (i < nq + nk) sq_k += v * v;
+  for (int i = V * threadIdx.x; i < n; i += V * blockDim.x) {
+    const Run<T, V> raw = *reinterpret_cast<const Run<T, V>*>(row + i);
+    float v[V], sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < V; ++k) v[k] = to_float<T>(raw.v[k]);
+    if (bias) {
+#pragma unroll
+      for (int k = 0; k < V; k += W) {
+        const Run<float, W> b = *reinterpret_cast<const Run<float, W>*>(bias + i + k);
+#pragma unroll
+        for (int m = 0; m < W; ++m) v[k + m] += b.v[m];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < V; k += W) {
+      Run<float, W> o;
+#pragma unroll
+      for (int m = 0; m < W; ++m) {
+        o.v[m] = v[k + m];
+        sq += v[k + m] * v[k + m];
+      }
+      *reinterpret_cast<Run<float, W>*>(row_s + i + k) = o;
+    }
+    if (i < nq) sq_q += sq;
+    else if (i < nq + nk) sq_k += sq;
   }
   float rq = 1.f, rk = 1.f;
   if (gain) {
@@ -110,10 +133,21 @@ __global__ void bias_row_norm_kernel(T* proj, int stride, int q0, int k0, int v0
   } else {
     __syncthreads();
   }
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = row_s[i];
-    if (gain && i < nq + nk) v *= (i < nq ? rq : rk) * gain[i];
-    row[i] = from_float<T>(v);
+  for (int i = V * threadIdx.x; i < n; i += V * blockDim.x) {  // every thread reads back what it wrote
+    Run<T, V> o;
+    const bool normed = gain && i < nq + nk;
+    const float r = i < nq ? rq : rk;
+#pragma unroll
+    for (int k = 0; k < V; k += W) {
+      const Run<float, W> v = *reinterpret_cast<const Run<float, W>*>(row_s + i + k);
+      Run<float, W> g;
+#pragma unroll
+      for (int m = 0; m < W; ++m) g.v[m] = 1.f;
+      if (normed) g = *reinterpret_cast<const Run<float, W>*>(gain + i + k);
+#pragma unroll
+      for (int m = 0; m < W; ++m) o.v[k + m] = from_float<T>(normed ? v.v[m] * r * g.v[m] : v.v[m]);
+    }
+    *reinterpret_cast<Run<T, V>*>(row + i) = o;
   }
 }
 
@@ -147,15 +181,19 @@ KRK_API int krk_bias_row_norm(void* proj, int stride, int q0, int k0, int v0, in
   const int n = end - q0;
   const size_t smem = (size_t)n * sizeof(float);
   if (smem > 200 * 1024) return -2;
-  const int threads = n >= 4096 ? 512 : (n >= 1024 ? 256 : 128);
+  const int V = dtype == KRK_DTYPE_F32 ? 4 : 8;
+  const bool vec = (k0 - q0) % V == 0 && (v0 - k0) % V == 0 && n % V == 0 && stride % V == 0 && q0 % V == 0 &&
+                   (((uintptr_t)proj | (uintptr_t)bias | (uintptr_t)gain) & 15) == 0;
+  const int pieces = vec ? n / V : n;
+  const int threads = pieces >= 4096 ? 512 : (pieces >= 1024 ? 256 : 128);
   if (dtype == KRK_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(bias_row_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return (int)launch_pdl(bias_row_norm_kernel<float>, dim3(rows), dim3(threads), smem, stream, (float*)proj, stride, q0,
-                           k0, v0, end, bias, gain, eps);
+    auto kern = vec ? bias_row_norm_kernel<float, 4> : bias_row_norm_kernel<float, 1>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (float*)proj, stride, q0, k0, v0, end, bias,
+                           gain, eps);
   }
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(bias_row_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return (int)launch_pdl(bias_row_norm_kernel<bf16>, dim3(rows), dim3(threads), smem, stream, (bf16*)proj, stride, q0, k0,
-                         v0, end, bias, gain, eps);
+  auto kern = vec ? bias_row_norm_kernel<bf16, 8> : bias_row_norm_kernel<bf16, 1>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (bf16*)proj, stride, q0, k0, v0, end, bias, gain,
+                         eps);
 }
