@@ -9,10 +9,11 @@
 // krk_ssd_scan: per (sequence, head), with S [N, P] float32 carried from token to token,
 //   dt = softplus(dt_raw + dt_bias_h);  a = exp(-exp(A_log_h) * dt)
 //   S <- a S + dt B x^T;  y = S^T C + D_h x
-// A block holds one head's state in registers: column p of S is spread over NS lanes of one warp, each holding
-// a run of consecutive rows; a token's y_p is each lane's partial sum (four ordered sums, added) followed by a
-// fixed exchange between the NS lanes. Tokens are staged through shared memory sixteen at a time (x, B, C as
-// float32, dt and a computed once per token). Steps of one sequence's many tokens run in three passes so that
+// A block holds one head's state in registers: a group of one, two or four columns of S is spread over NS lanes
+// of one warp, each holding a run of consecutive rows of those columns; a token's y_p is each lane's ordered
+// partial sums followed by a fixed exchange between the NS lanes. Tokens are staged through shared memory sixteen
+// at a time (x, B, C as float32, dt and a computed once per token), the next sixteen requested as asynchronous
+// copies while these are computed. Steps of one sequence's many tokens run in three passes so that
 // all SMs work on one sequence: every chunk of `chunk` tokens scans from a zero state to its local end state
 // (pass 1), one small kernel walks a sequence's chunks in order, S_in[c+1] = (prod a) S_in[c] + local[c], and
 // leaves every chunk its starting state and the sequence its final one (pass 2), and every chunk scans again
