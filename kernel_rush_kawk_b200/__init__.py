@@ -1,5 +1,6 @@
 """A small B200-native inference library for the Qwen3 dense decoder, the Taredra hybrid decoder,
-the Disorax latent-attention mixture-of-experts decoder and the Zadunex state-space hybrid decoder.
+the Disorax latent-attention mixture-of-experts decoder, the Zadunex state-space hybrid decoder and the
+Fogizen decoder (chunked attention with mixed head scores beside time mixing, routed experts).
 
 From a model folder (config.json + safetensors) or seeded random weights to
 generated tokens on one GPU: typed configuration and registry, weights by
@@ -8,11 +9,11 @@ function, a generation loop with greedy and temperature sampling, and trace
 replay. All arithmetic of the model runs in this package's own CUDA kernels.
 """
 
-from .config import ConfigError, DisoraxConfig, Qwen3Config, TaredraConfig, ZadunexConfig, read_config, register_architecture
+from .config import ConfigError, DisoraxConfig, FogizenConfig, Qwen3Config, TaredraConfig, ZadunexConfig, read_config, register_architecture
 from .engine import Engine, StepEntry
 from .sampling import SamplingParams
 from .weights import WeightError, write_model_folder
 
 __version__ = "0.1.0"
-__all__ = ["ConfigError", "DisoraxConfig", "Qwen3Config", "TaredraConfig", "ZadunexConfig", "read_config", "register_architecture", "Engine", "StepEntry",
+__all__ = ["ConfigError", "DisoraxConfig", "FogizenConfig", "Qwen3Config", "TaredraConfig", "ZadunexConfig", "read_config", "register_architecture", "Engine", "StepEntry",
            "SamplingParams", "WeightError", "write_model_folder"]

@@ -83,7 +83,7 @@ class _StateGroup:
     def __init__(self, need: StateNeed, runs: list[int], n_slots: int, device, dtype):
         self.need = need
         self.runs = runs
-        dt = torch.float32 if need.dtype == "float32" else dtype
+        dt = {"float32": torch.float32, "int32": torch.int32}.get(need.dtype, dtype)
         self.state = torch.zeros((len(runs), n_slots) + tuple(need.shape), dtype=dt, device=device)
 
 

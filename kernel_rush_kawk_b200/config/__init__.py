@@ -5,6 +5,7 @@ from .qwen3 import Qwen3Config
 from .taredra import TaredraConfig
 from .disorax import DisoraxConfig
 from .zadunex import ZadunexConfig
+from .fogizen import FogizenConfig
 from .registry import (Architecture, architecture_name, get_architecture, known_architectures, preset_config,
                        read_config, register_architecture)
 

@@ -92,4 +92,4 @@ def _load_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import disorax, qwen3, taredra, zadunex  # noqa: F401  (each registers itself on import)
+        from ..models import disorax, fogizen, qwen3, taredra, zadunex  # noqa: F401  (each registers itself on import)

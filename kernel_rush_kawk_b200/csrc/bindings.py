@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_uint, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
 
 import torch
 
@@ -66,9 +66,19 @@ _MIX_SIGNATURES = {
                                   c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "krk_latent_norm_write": [_P, c_int, c_int, c_int, _P, c_float, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_int, _P],
     "krk_head_linear": [_P, c_int, c_int, c_float, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_embed_bigram": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, _P, _P, _P, _P, _P, c_int, _P],
+    "krk_bias_norm_rotate_write": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, _P, c_int,
+                                   c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, _P],
+    "krk_mixed_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P,
+                            c_int, _P, _P, c_int, c_float, c_int, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_mixed_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+                                   _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_norm_sum": [_P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_float, c_float, c_int, _P],
+    "krk_act_rows": [_P, _P, c_int, c_int, c_int, c_int, c_float, c_float, c_int, _P],
 }
 _MOE_SIGNATURES = {
     "krk_moe_route": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_int],
+    "krk_moe_route_groups": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "krk_moe_gate_up_pairs": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_moe_down_pairs": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_moe_sort": [_P, _P, _P, c_int, c_int, c_int, _P],
@@ -76,7 +86,7 @@ _MOE_SIGNATURES = {
     "krk_moe_combine": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
 }
 _SCAN_SIGNATURES = {
-    "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
+    "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
                               c_int, _P, _P, _P, c_int, _P, _P, c_int, _P],
@@ -85,7 +95,7 @@ _SCAN_SIGNATURES = {
                      c_int, _P, _P, _P, c_int, _P, _P, c_int, _P],
     "krk_gated_group_norm": [_P, c_int, c_int, c_float, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, _P],
 }
-_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2, "swish_clamped": 3}
+_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2, "swish_clamped": 3, "xielu": 4}
 _ATTN_SIGNATURES = {
     "krk_attention_simple": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
     "krk_attention_head_dim": [],
@@ -611,17 +621,27 @@ class Kernels:
     # -- routed experts ------------------------------------------------------------------------
     MOE_PAIR_ROWS = 16  # rows up to which every (row, expert) pair reads its expert's weights by itself
 
-    def moe_route(self, x, w, b, top, gate_row=False, over_all=False):
+    def moe_route(self, x, w, b, top, gate_row=False, over_all=False, sigmoid_groups=None):
         """(experts int32 [rows, top], weights float32 [rows, top], row gate float32 [rows] or None): the ``top`` largest
         of x W^T + b in 32-bit (ties: the lower index) and the softmax over them, or with ``over_all`` their shares of
         the softmax over all experts. With ``gate_row`` the last row of W is no expert but a gate's weights: sigmoid
-        of its product is the row gate."""
+        of its product is the row gate. ``sigmoid_groups`` = (correction, groups, keep, scale): sigmoid scores, the choice
+        by score + correction among the experts of the ``keep`` best of ``groups`` groups of neighbours, the weights
+        the chosen scores over their sum, times ``scale``."""
         E = w.shape[0] - int(gate_row)
         rows, K = x.shape
         experts = torch.empty((rows, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((rows, top), dtype=torch.float32, device=x.device)
         row_gate = torch.empty(rows, dtype=torch.float32, device=x.device) if gate_row else None
         logits = self.linear(x, w, out_float32=True)
+        if sigmoid_groups is not None:
+            correction, groups, keep, scale = sigmoid_groups
+            if correction.dtype != torch.float32 or correction.numel() != E:
+                raise KernelError("the routing correction is one float32 number per expert")
+            self._ok(self.moe.krk_moe_route_groups(experts.data_ptr(), weights.data_ptr(), _ptr(row_gate), logits.data_ptr(),
+                                                   correction.data_ptr(), rows, E, int(gate_row), int(top), int(groups),
+                                                   int(keep), float(scale), self._stream()), "expert routing within groups")
+            return experts, weights, row_gate
         self._ok(self.moe.krk_moe_route(experts.data_ptr(), weights.data_ptr(), _ptr(row_gate), logits.data_ptr(), _ptr(b),
                                         rows, E, int(gate_row), int(top), self._stream(), int(over_all)), "expert routing")
         return experts, weights, row_gate
@@ -784,14 +804,112 @@ class Kernels:
             cache.width, cache.k.data_ptr(), cache.v.data_ptr(), proj.shape[0], float(scale), int(window or 0),
             *extras, _code(proj.dtype), self._stream()), "windowed attention with a sink")
 
-    def token_shift(self, h, last_state, mu, batch):
-        """[mixes, rows, hidden]: h + (h_prev - h) * mu, the row before a step's first coming from ``last_state``."""
+    # -- pair-hash embedding, per-head norms with pair rotation, mixed head scores over blocks of keys ------------
+    def embed_bigram(self, table, pairs, state, buckets, mul_prev, mul_cur, batch):
+        """float32 rows table[id] + pairs[(id_prev * mul_prev + id * mul_cur) % buckets] (row ``buckets`` at position 0);
+        ``state`` int32 [slots, 1] holds every sequence's last token and is brought up to date."""
+        if state.dtype != torch.int32 or not state.is_contiguous() or pairs.dtype != table.dtype or pairs.shape[0] != buckets + 1:
+            raise KernelError("the pair embedding keeps one int32 per slot and a second table of buckets + 1 rows")
+        rows = batch.n_rows
+        out = torch.empty((rows, table.shape[1]), dtype=torch.float32, device=table.device)
+        self._ok(self.mix.krk_embed_bigram(out.data_ptr(), table.data_ptr(), pairs.data_ptr(), batch.tokens.data_ptr(),
+                                           state.data_ptr(), rows, table.shape[1], table.shape[0], int(buckets), int(mul_prev),
+                                           int(mul_cur), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(),
+                                           batch.cu_q.data_ptr(), batch.seq_slot.data_ptr(), self.error.data_ptr(),
+                                           _code(table.dtype), self._stream()), "pair-hash embedding")
+        return out
+
+    def bias_norm_rotate_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, bias, qk_gain, eps, inv_freq,
+                               rot_dims, pairs, batch, cache):
+        """On a stacked q | k | v product: float32 ``bias`` over all three (None: none); with ``qk_gain`` (float32, the q
+        weight then the k weight, ``dim`` each) every q and k head is divided by its root mean square and multiplied by
+        it; the first ``rot_dims`` elements are rotated (``pairs``: 2i with 2i + 1, else i with i + rot_dims/2); q in
+        place, k and v into their pages."""
+        ptr, stride = self._rows_view(proj)
+        if cache.k.dtype != proj.dtype or cache.head_dim != dim or cache.v_dim != vdim or cache.kv_heads != kv_heads:
+            raise KernelError("the cache does not fit the heads it is to receive")
+        n = (heads + kv_heads) * dim + kv_heads * vdim
+        if (bias is not None and (bias.numel() != n or bias.dtype != torch.float32)) or (
+                qk_gain is not None and (qk_gain.numel() != 2 * dim or qk_gain.dtype != torch.float32)):
+            raise KernelError("float32 biases cover q, k and v; the float32 gains are one head's q weight and k weight")
+        self._ok(self.mix.krk_bias_norm_rotate_write(
+            ptr, stride, q_col, k_col, v_col, heads, kv_heads, dim, vdim, _ptr(bias), _ptr(qk_gain), float(eps),
+            inv_freq.data_ptr(), int(rot_dims), int(bool(pairs)), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(),
+            batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
+            proj.shape[0], int(getattr(cache, "keep_pages", 0)), _code(proj.dtype), self._stream()),
+            "biases + head norms + rotation + cache write")
+
+    MIXED_SPLITS_MAX = 8  # blocks that share one sequence's keys in a single-token step
+
+    def mixed_attention(self, proj, q_col, heads, dim, vdim, sink, talk, scale, chunk, batch, cache, out, out_col, out_scale,
+                        gate=None):
+        """Attention over the keys of the query's own block of ``chunk`` positions (None: all earlier keys), the heads'
+        scores mixed by ``talk`` [heads, heads] before the softmax (None: not mixed), ``sink`` as in ``sink_attention``,
+        ``gate`` (column, "head"). Up to 32 heads, value heads up to 256."""
+        ptr, stride = self._rows_view(proj)
+        optr, ostride = self._rows_view(out)
+        g_col, g_mode = (int(gate[0]), 1) if gate is not None else (0, 0)
+        if gate is not None and gate[1] != "head":
+            raise KernelError("this attention takes a gate per head only")
+        if getattr(cache, "keep_pages", 0) or cache.window:
+            raise KernelError("this attention reads a cache that keeps every key")
+        if talk is not None and (talk.dtype != torch.float32 or talk.shape != (heads, heads) or not talk.is_contiguous()):
+            raise KernelError("the heads' mixing matrix is float32 [heads, heads]")
+        chunk = int(chunk or 0)
+        if batch.is_decode and proj.shape[0] == batch.n_seqs:
+            # by the step's shape alone, never by lengths, so that a captured step stays valid
+            most = -(-chunk // 32) if chunk else self.MIXED_SPLITS_MAX
+            splits = max(1, min(self.MIXED_SPLITS_MAX, most, 148 // batch.n_seqs))
+            key = ("mixed", batch.n_seqs, heads, vdim, splits)
+            scratch = self._partials.get(key)
+            if scratch is None:
+                scratch = self._partials[key] = torch.empty(batch.n_seqs * heads * splits * (vdim + 2), dtype=torch.float32,
+                                                            device=self.device)
+            self._ok(self.mix.krk_mixed_attention_single(
+                optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),
+                _ptr(talk), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
+                cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, float(scale), chunk, splits, scratch.data_ptr(),
+                ptr, stride, g_col, g_mode, _code(proj.dtype), self._stream()), "single-token attention with mixed scores")
+            self.launches += 1
+            return
+        self._ok(self.mix.krk_mixed_attention(
+            optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),
+            _ptr(talk), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(),
+            cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(), proj.shape[0], float(scale), chunk,
+            ptr, stride, g_col, g_mode, _code(proj.dtype), self._stream()), "attention with mixed scores")
+
+    def norm_sum(self, outs, gains, eps, scale):
+        """scale * sum_b rmsnorm(outs[b]) * gains[b]: up to four [rows, C] inputs of the path's dtype, float32 gains [n, C]."""
+        first = outs[0]
+        n = len(outs)
+        if any(o.shape != first.shape or o.dtype != first.dtype or not o.is_contiguous() for o in outs) or (
+                gains.dtype != torch.float32 or gains.shape != (n, first.shape[1]) or not gains.is_contiguous()):
+            raise KernelError("the summed norms read contiguous rows of one shape and dtype and float32 gains [n, C]")
+        out = torch.empty_like(first)
+        ptrs = [o.data_ptr() for o in outs] + [None] * (4 - n)
+        self._ok(self.mix.krk_norm_sum(out.data_ptr(), *ptrs, n, gains.data_ptr(), first.shape[0], first.shape[1], float(eps),
+                                       float(scale), _code(first.dtype), self._stream()), "norms of several outputs, summed")
+        return out
+
+    def act_rows(self, z, activation, params=(0.0, 0.0)):
+        """An activation without a gate over [rows, I]; "xielu" takes (softplus(p), 1/2 + softplus(q))."""
+        ptr, stride = self._rows_view(z)
+        out = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+        self._ok(self.mix.krk_act_rows(out.data_ptr(), ptr, stride, z.shape[0], z.shape[1], _ACTIVATIONS[activation],
+                                       float(params[0]), float(params[1]), _code(z.dtype), self._stream()), "activation")
+        return out
+
+    def token_shift(self, h, last_state, mu, batch, store=False):
+        """[mixes, rows, hidden]: h + (h_prev - h) * mu, the row before a step's first coming from ``last_state``;
+        with ``store`` every sequence's last row of the step then takes its place there."""
+        if last_state.dtype != torch.float32 or not last_state.is_contiguous() or mu.dtype != torch.float32:
+            raise KernelError("the token shift keeps a contiguous float32 row per slot and reads float32 blend weights")
         ptr, stride = self._rows_view(h)
         rows, C = h.shape
         out = torch.empty((mu.shape[0], rows, C), dtype=h.dtype, device=h.device)
         self._ok(self.scan.krk_token_shift(out.data_ptr(), ptr, stride, last_state.data_ptr(), mu.data_ptr(), mu.shape[0],
                                           C, rows, batch.row_seq.data_ptr(), batch.cu_q.data_ptr(),
-                                          batch.seq_slot.data_ptr(), _code(h.dtype), self._stream()), "token shift")
+                                          batch.seq_slot.data_ptr(), _code(h.dtype), self._stream(), int(store)), "token shift")
         return out
 
     def linear_recurrence(self, kind, r, k, v, gate, lora, w2, w0, heads, dim, norm_w, eps, state, batch, out, out_col,

@@ -32,7 +32,7 @@ SRC_DIR = Path(__file__).parent
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu", "lt_gemm.cu"]
 CORE_LIBS = ["-lcublasLt"]  # lt_gemm.cu; the process already holds the copy that torch loaded
-MIX_SOURCES = ["wide_rows.cu", "sink_attention.cu", "latent.cu", "hyper.cu"]
+MIX_SOURCES = ["wide_rows.cu", "sink_attention.cu", "latent.cu", "hyper.cu", "mixed_attention.cu"]
 SCAN_SOURCES = ["recurrent.cu", "ssd.cu"]
 MOE_SOURCES = ["routed.cu"]
 SMALL_LIBRARIES = {"mix": MIX_SOURCES, "scan": SCAN_SOURCES, "moe": MOE_SOURCES}

@@ -1,0 +1,522 @@
+// Attention whose heads' scores are mixed before the softmax, over the keys of the query's own block of
+// positions, and the row kernels that a model built around it needs.
+//
+// krk_embed_bigram: x[r] = table[id_r] + pairs[(id_prev * a + id_r * b) mod m] (row m for a sequence's first token),
+// float32 rows. id_prev of a step's first row is the sequence's stored last token; the block of that row reads it
+// and then stores the step's last token in its place.
+//
+// krk_bias_norm_rotate_write: one warp per (row, head) of a stacked q | k | v product. Biases are added; a q or k
+// head is divided by its root mean square and multiplied by a weight of the head's size (shared by the heads); the
+// first `rot` elements are rotated by the position, element 2i with 2i + 1 (`pairs`) or i with i + rot/2; q is
+// written back in place, k and v go to their pages. All arithmetic is float32 and a value is rounded once. The
+// angle's sine and cosine are those of csrc/sink_attention.cu (frequencies as two floats each).
+//
+// krk_mixed_attention: one block per row, one warp per query head. The warps take 32 keys at a time, one key per
+// lane: each lane's raw score is its own ordered sum over the head; the warps exchange their raw scores through
+// shared memory and warp h forms s'_h = sum_g talk[h, g] s_g (g ascending); the softmax runs online with the sink
+// as the starting state (maximum = sink, sum = 1, no value), and the float32 weights multiply the values with the
+// lanes spread over the value head. A query at position p sees keys (p / chunk) * chunk .. p (chunk 0: 0 .. p). A
+// row's result depends on that row's keys only, in their order: it is the same to the bit however the tokens were
+// cut into steps or batched. Without `talk` no scores are exchanged.
+//
+// krk_mixed_attention_single (one token per sequence): the keys of a sequence are split over the blocks of a
+// cluster-free grid (sequence, split); every block does what the general kernel does over its share of the 32-key
+// chunks and leaves (maximum, sum, output) per head; krk_mixed_attention_merge adds the shares in split order. The
+// sink enters once, in the first split.
+//
+// krk_norm_sum: out = scale * sum_b y_b / sqrt(mean(y_b^2) + eps) * gain_b over up to four inputs, float32 inside.
+// krk_act_rows: an activation without a gate, elementwise (xIELU with its two slopes, tanh-GELU, SiLU).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+__device__ __forceinline__ void angle_sincos2(float p, float f_hi, float f_lo, float* s, float* c) {
+  const float a = __fmul_rn(p, f_hi);
+  const float e = fmaf(p, f_hi, -a) + p * f_lo;
+  float s0, c0;
+  sincosf(a, &s0, &c0);
+  *s = fmaf(e, c0, s0);
+  *c = fmaf(-e, s0, c0);
+}
+
+template <typename T>
+__global__ void embed_bigram_kernel(float* __restrict__ out, const T* __restrict__ table, const T* __restrict__ pairs,
+                                    const int* __restrict__ ids, int* state, int H, int vocab, int buckets,
+                                    long long mul_prev, long long mul_cur, const int* __restrict__ row_seq,
+                                    const int* __restrict__ row_pos, const int* __restrict__ cu_q,
+                                    const int* __restrict__ seq_slot, int* error) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const int seq = row_seq[r];
+  const int first_row = cu_q[seq];
+  const int slot = seq_slot[seq];
+  int id = ids[r];
+  int prev = r == first_row ? state[slot] : ids[r - 1];
+  const bool bad = id < 0 || id >= vocab || prev < 0 || prev >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0 && error) atomicExch(error, 1);
+    id = prev = 0;
+  }
+  const long long bucket = row_pos[r] == 0 ? (long long)buckets : (prev * mul_prev + id * mul_cur) % buckets;
+  const T* a = table + (size_t)id * H;
+  const T* b = pairs + (size_t)bucket * H;
+  float* dst = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = bad ? 0.f : to_float<T>(a[i]) + to_float<T>(b[i]);
+  if (r == first_row) {
+    __syncthreads();  // every thread of this block has read the stored token
+    if (threadIdx.x == 0) state[slot] = ids[cu_q[seq + 1] - 1];
+  }
+}
+
+template <typename T>
+__global__ void bias_norm_rotate_write_kernel(T* proj, int stride, int q_col, int k_col, int v_col, int HQ, int HKV, int D,
+                                              int DV, const float* __restrict__ bias, const float* __restrict__ gain,
+                                              float eps, const float* __restrict__ inv_freq, int rot, int pairs,
+                                              const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                              const int* __restrict__ seq_slot, const int* __restrict__ table, int width,
+                                              T* k_cache, T* v_cache, int rows, int keep_pages) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int per_row = HQ + 2 * HKV;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)rows * per_row) return;
+  const int row = (int)(item / per_row), which = (int)(item % per_row);
+  const int pos = row_pos[row];
+  T* base = proj + (size_t)row * stride;
+  const T* src;
+  T* dst;
+  const float* b = bias;
+  const float* g = nullptr;
+  int n, turn;
+  if (which < HQ) {
+    src = dst = base + q_col + (size_t)which * D;
+    if (b) b += (size_t)which * D;
+    g = gain;
+    n = D;
+    turn = rot;
+  } else {
+    const int slot = seq_slot[row_seq[row]];
+    const int page = page_of(table, width, slot, pos, keep_pages);
+    if (which < HQ + HKV) {
+      const int h = which - HQ;
+      src = base + k_col + (size_t)h * D;
+      dst = k_cache + (((size_t)page * HKV + h) * KRK_PAGE + (pos % KRK_PAGE)) * D;
+      if (b) b += (size_t)HQ * D + (size_t)h * D;
+      g = gain ? gain + D : nullptr;
+      n = D;
+      turn = rot;
+    } else {
+      const int h = which - HQ - HKV;
+      src = base + v_col + (size_t)h * DV;
+      dst = v_cache + (((size_t)page * HKV + h) * KRK_PAGE + (pos % KRK_PAGE)) * DV;
+      if (b) b += (size_t)(HQ + HKV) * D + (size_t)h * DV;
+      n = DV;
+      turn = 0;
+    }
+  }
+  float rstd = 1.f;
+  if (g) {
+    float sq = 0.f;
+    for (int e = lane; e < n; e += 32) {
+      const float x = to_float<T>(src[e]) + (b ? b[e] : 0.f);
+      sq += x * x;
+    }
+    rstd = rsqrtf(warp_sum(sq) / (float)n + eps);
+  }
+  __syncwarp();  // q is rewritten in place: every lane has read what it needs of the head
+  auto val = [&](int e) { return (to_float<T>(src[e]) + (b ? b[e] : 0.f)) * rstd * (g ? g[e] : 1.f); };
+  const int half = turn >> 1;
+  const float p = (float)pos;
+  for (int i = lane; i < half; i += 32) {
+    const int e0 = pairs ? 2 * i : i, e1 = pairs ? 2 * i + 1 : i + half;
+    float s, c;
+    angle_sincos2(p, inv_freq[i], inv_freq[half + i], &s, &c);
+    const float u = val(e0), v = val(e1);
+    dst[e0] = from_float<T>(u * c - v * s);
+    dst[e1] = from_float<T>(v * c + u * s);
+  }
+  for (int e = turn + lane; e < n; e += 32) dst[e] = from_float<T>(val(e));
+}
+
+template <typename T> __device__ __forceinline__ float dot_key(const float* q, const T* k, int D) {
+  float dot = 0.f;
+  for (int d = 0; d < D; ++d) dot += q[d] * to_float<T>(k[d]);
+  return dot;
+}
+// bfloat16 rows of a multiple of 8 elements start on 16-byte boundaries in the cache
+template <> __device__ __forceinline__ float dot_key<bf16>(const float* q, const bf16* k, int D) {
+  float dot = 0.f;
+  if ((D & 7) == 0) {
+    for (int d = 0; d < D; d += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        dot += q[d + 2 * j] * __low2float(p[j]);
+        dot += q[d + 2 * j + 1] * __high2float(p[j]);
+      }
+    }
+  } else {
+    for (int d = 0; d < D; ++d) dot += q[d] * __bfloat162float(k[d]);
+  }
+  return dot;
+}
+
+constexpr int MIX_VPL = 8;  // value heads up to 256
+
+// The walk of one warp (= one query head of one row) over the 32-key chunks base = lo + 32 * (c0 + n * cstep), up to hi,
+// together with the block's other warps. Leaves the running (m, l, acc).
+template <typename T>
+__device__ __forceinline__ void mixed_walk(const float* qs, float* s_buf, const float* talk_s, int HQ, int HKV, int head,
+                                           int D, int DV, int slot, int lo, int hi, int c0, int cstep,
+                                           const int* __restrict__ table, int width, const T* __restrict__ k_cache,
+                                           const T* __restrict__ v_cache, float scale, float& m, float& l, float* acc) {
+  const int lane = threadIdx.x & 31;
+  const int kh = head / (HQ / HKV);
+  int it = 0;
+  for (int base = lo + 32 * c0; base <= hi; base += 32 * cstep, ++it) {
+    const int key = base + lane;
+    const bool valid = key <= hi;
+    float s = 0.f;
+    int my_page = 0;
+    if (valid) {
+      my_page = page_of(table, width, slot, key);
+      s = dot_key<T>(qs, k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D, D) * scale;
+    }
+    if (talk_s) {
+      // two buffers in turn: a warp that runs ahead writes the other buffer, and cannot lap (one barrier a chunk)
+      float* buf = s_buf + (size_t)(it & 1) * HQ * 32;
+      buf[head * 32 + lane] = s;
+      __syncthreads();
+      float mixed = 0.f;
+      for (int g = 0; g < HQ; ++g) mixed += talk_s[head * HQ + g] * buf[g * 32 + lane];
+      s = mixed;
+    }
+    if (!valid) s = -INFINITY;
+    const float m_new = fmaxf(m, warp_max(s));
+    const float alpha = expf(m - m_new);  // exp(-inf) = 0 before the first key when there is no sink
+    const float p = valid ? expf(s - m_new) : 0.f;
+    l = l * alpha + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < MIX_VPL; ++i) acc[i] *= alpha;
+    const int n = min(32, hi - base + 1);
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const int page = __shfl_sync(0xffffffffu, my_page, j);  // lane j looked its key's page up already
+      const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + ((base + j) % KRK_PAGE)) * DV;
+#pragma unroll
+      for (int i = 0; i < MIX_VPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < DV) acc[i] += pj * to_float<T>(vp[d]);
+      }
+    }
+    m = m_new;
+  }
+}
+
+template <typename T>
+__global__ void mixed_attention_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
+                                       const T* __restrict__ proj, int stride, int q_col, int HQ, int HKV, int D, int DV,
+                                       const float* __restrict__ sink, const float* __restrict__ talk,
+                                       const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                       const int* __restrict__ seq_slot, const int* __restrict__ table, int width,
+                                       const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale, int chunk,
+                                       const T* __restrict__ gate, int gate_stride, int gate_col, int gate_mode) {
+  extern __shared__ __align__(16) float sm_mix[];
+  float* q_s = sm_mix;                               // [HQ][D]
+  float* s_buf = q_s + ((HQ * D + 3) & ~3);          // [2][HQ][32]
+  float* talk_s = s_buf + 2 * HQ * 32;               // [HQ][HQ]
+  if (talk)
+    for (int i = threadIdx.x; i < HQ * HQ; i += blockDim.x) talk_s[i] = talk[i];  // weights: before the wait
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, head = threadIdx.x >> 5;
+  const int row = blockIdx.x;
+  const int pos = row_pos[row];
+  const int slot = seq_slot[row_seq[row]];
+  const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+  const T* q = proj + (size_t)row * stride + q_col;
+  for (int i = threadIdx.x; i < HQ * D; i += blockDim.x) q_s[i] = to_float<T>(q[i]);
+  __syncthreads();
+  float m = sink ? sink[head] : -INFINITY;
+  float l = sink ? 1.f : 0.f;
+  float acc[MIX_VPL];
+#pragma unroll
+  for (int i = 0; i < MIX_VPL; ++i) acc[i] = 0.f;
+  mixed_walk<T>(q_s + (size_t)head * D, s_buf, talk ? talk_s : nullptr, HQ, HKV, head, D, DV, slot, lo, pos, 0, 1, table,
+                width, k_cache, v_cache, scale, m, l, acc);
+  T* o = out + (size_t)row * out_stride + out_col + (size_t)head * DV;
+  float inv = out_scale / l;
+  if (gate_mode == 1) inv *= sigmoid_(to_float<T>(gate[(size_t)row * gate_stride + gate_col + head]));
+#pragma unroll
+  for (int i = 0; i < MIX_VPL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < DV) o[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+// One token per sequence: block (split, sequence) takes every SPL-th 32-key chunk and leaves its share in
+// scratch [seq][head][SPL][DV + 2] as (m, l, acc[DV]).
+template <typename T>
+__global__ void mixed_attention_single_kernel(float* __restrict__ scratch, const T* __restrict__ proj, int stride, int q_col,
+                                              int HQ, int HKV, int D, int DV, const float* __restrict__ sink,
+                                              const float* __restrict__ talk, const int* __restrict__ seq_slot,
+                                              const int* __restrict__ seq_start, const int* __restrict__ table, int width,
+                                              const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale,
+                                              int chunk, int SPL) {
+  extern __shared__ __align__(16) float sm_mix[];
+  float* q_s = sm_mix;
+  float* s_buf = q_s + ((HQ * D + 3) & ~3);
+  float* talk_s = s_buf + 2 * HQ * 32;
+  if (talk)
+    for (int i = threadIdx.x; i < HQ * HQ; i += blockDim.x) talk_s[i] = talk[i];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, head = threadIdx.x >> 5;
+  const int split = blockIdx.x, seq = blockIdx.y;
+  const int pos = seq_start[seq];  // the one new token sits at the sequence's length before the step
+  const int slot = seq_slot[seq];
+  const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+  const T* q = proj + (size_t)seq * stride + q_col;
+  for (int i = threadIdx.x; i < HQ * D; i += blockDim.x) q_s[i] = to_float<T>(q[i]);
+  __syncthreads();
+  const bool with_sink = sink && split == 0;
+  float m = with_sink ? sink[head] : -INFINITY;
+  float l = with_sink ? 1.f : 0.f;
+  float acc[MIX_VPL];
+#pragma unroll
+  for (int i = 0; i < MIX_VPL; ++i) acc[i] = 0.f;
+  mixed_walk<T>(q_s + (size_t)head * D, s_buf, talk ? talk_s : nullptr, HQ, HKV, head, D, DV, slot, lo, pos, split, SPL,
+                table, width, k_cache, v_cache, scale, m, l, acc);
+  float* dst = scratch + (((size_t)seq * HQ + head) * SPL + split) * (DV + 2);
+  if (lane == 0) {
+    dst[0] = m;
+    dst[1] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < MIX_VPL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < DV) dst[2 + d] = acc[i];
+  }
+}
+
+// one warp per (sequence, head): the splits' shares in split order
+template <typename T>
+__global__ void mixed_attention_merge_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
+                                             const float* __restrict__ scratch, int HQ, int DV, int SPL, int n_seqs,
+                                             const T* __restrict__ gate, int gate_stride, int gate_col, int gate_mode) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= n_seqs * HQ) return;
+  const int seq = item / HQ, head = item % HQ;
+  const float* src = scratch + (size_t)item * SPL * (DV + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < SPL; ++s) m = fmaxf(m, src[(size_t)s * (DV + 2)]);
+  float l = 0.f, acc[MIX_VPL];
+#pragma unroll
+  for (int i = 0; i < MIX_VPL; ++i) acc[i] = 0.f;
+  for (int s = 0; s < SPL; ++s) {
+    const float* p = src + (size_t)s * (DV + 2);
+    const float w = expf(p[0] - m);  // a split without keys left (-inf, 0, 0): weight 0
+    l += w * p[1];
+#pragma unroll
+    for (int i = 0; i < MIX_VPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < DV) acc[i] += w * p[2 + d];
+    }
+  }
+  float inv = out_scale / l;
+  if (gate_mode == 1) inv *= sigmoid_(to_float<T>(gate[(size_t)seq * gate_stride + gate_col + head]));
+  T* o = out + (size_t)seq * out_stride + out_col + (size_t)head * DV;
+#pragma unroll
+  for (int i = 0; i < MIX_VPL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < DV) o[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+struct NormSumArgs {
+  const void* y[4];
+  const float* gain;  // [n][C]
+  int n;
+};
+
+template <typename T>
+__global__ void norm_sum_kernel(T* __restrict__ out, NormSumArgs a, int C, float eps, float scale) {
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const size_t row = blockIdx.x;
+  float rstd[4];
+  for (int b = 0; b < a.n; ++b) {
+    const T* y = reinterpret_cast<const T*>(a.y[b]) + row * C;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      const float v = to_float<T>(y[c]);
+      sq += v * v;
+    }
+    rstd[b] = rsqrtf(block_sum(sq, scratch) / (float)C + eps);
+  }
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float total = 0.f;
+    for (int b = 0; b < a.n; ++b)
+      total += to_float<T>(reinterpret_cast<const T*>(a.y[b])[row * C + c]) * rstd[b] * a.gain[(size_t)b * C + c];
+    out[row * C + c] = from_float<T>(total * scale);
+  }
+}
+
+// act 0: silu, 1: tanh-GELU, 4: xIELU with pa = softplus(p), pb = 1/2 + softplus(q)
+template <typename T>
+__global__ void act_rows_kernel(T* __restrict__ out, const T* __restrict__ z, int z_stride, int rows, int I, int act,
+                                float pa, float pb) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const long long total = (long long)rows * I;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / I;
+    const int c = (int)(i % I);
+    const float v = to_float<T>(z[r * z_stride + c]);
+    float y;
+    if (act == 4) y = v > 0.f ? pa * v * v + 0.5f * v : pb * (expm1f(v) - v) + 0.5f * v;
+    else if (act == 1) y = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    else y = v / (1.0f + expf(-v));
+    out[i] = from_float<T>(y);
+  }
+}
+
+size_t mixed_smem(int HQ, int D, bool talk) {
+  return (size_t)(((HQ * D + 3) & ~3) + (talk ? 2 * HQ * 32 + HQ * HQ : 0)) * sizeof(float);
+}
+
+}  // namespace
+
+KRK_API int krk_embed_bigram(float* out, const void* table, const void* pairs, const int* ids, int* state, int rows, int H,
+                             int vocab, int buckets, long long mul_prev, long long mul_cur, const int* row_seq,
+                             const int* row_pos, const int* cu_q, const int* seq_slot, int* error, int dtype,
+                             cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (buckets < 1) return -2;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(embed_bigram_kernel<float>, dim3(rows), dim3(128), 0, stream, out, (const float*)table,
+                           (const float*)pairs, ids, state, H, vocab, buckets, mul_prev, mul_cur, row_seq, row_pos, cu_q,
+                           seq_slot, error);
+  return (int)launch_pdl(embed_bigram_kernel<bf16>, dim3(rows), dim3(128), 0, stream, out, (const bf16*)table,
+                         (const bf16*)pairs, ids, state, H, vocab, buckets, mul_prev, mul_cur, row_seq, row_pos, cu_q,
+                         seq_slot, error);
+}
+
+KRK_API int krk_bias_norm_rotate_write(void* proj, int stride, int q_col, int k_col, int v_col, int HQ, int HKV, int D, int DV,
+                                       const float* bias, const float* gain, float eps, const float* inv_freq, int rot,
+                                       int pairs, const int* row_seq, const int* row_pos, const int* seq_slot,
+                                       const int* table, int width, void* k_cache, void* v_cache, int rows, int keep_pages,
+                                       int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rot < 0 || rot > D || (rot & 1)) return -2;
+  const long long items = (long long)rows * (HQ + 2 * HKV);
+  const int warps = 4;
+  const long long blocks = (items + warps - 1) / warps;
+  if (blocks > 0x7fffffffLL) return -3;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(bias_norm_rotate_write_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
+                           (float*)proj, stride, q_col, k_col, v_col, HQ, HKV, D, DV, bias, gain, eps, inv_freq, rot, pairs,
+                           row_seq, row_pos, seq_slot, table, width, (float*)k_cache, (float*)v_cache, rows, keep_pages);
+  return (int)launch_pdl(bias_norm_rotate_write_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
+                         (bf16*)proj, stride, q_col, k_col, v_col, HQ, HKV, D, DV, bias, gain, eps, inv_freq, rot, pairs,
+                         row_seq, row_pos, seq_slot, table, width, (bf16*)k_cache, (bf16*)v_cache, rows, keep_pages);
+}
+
+KRK_API int krk_mixed_attention(void* out, int out_stride, int out_col, float out_scale, const void* proj, int stride,
+                                int q_col, int HQ, int HKV, int D, int DV, const float* sink, const float* talk,
+                                const int* row_seq, const int* row_pos, const int* seq_slot, const int* table, int width,
+                                const void* k_cache, const void* v_cache, int rows, float scale, int chunk, const void* gate,
+                                int gate_stride, int gate_col, int gate_mode, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (HQ < 1 || HQ > 32 || HKV < 1 || HQ % HKV || DV > 32 * MIX_VPL || gate_mode > 1 || chunk < 0) return -2;
+  const size_t smem = mixed_smem(HQ, D, talk != nullptr);
+  if (smem > 200 * 1024) return -2;
+  if (dtype == KRK_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(mixed_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(mixed_attention_kernel<float>, dim3(rows), dim3(HQ * 32), smem, stream, (float*)out, out_stride,
+                           out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, row_seq, row_pos,
+                           seq_slot, table, width, (const float*)k_cache, (const float*)v_cache, scale, chunk,
+                           (const float*)gate, gate_stride, gate_col, gate_mode);
+  }
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(mixed_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(mixed_attention_kernel<bf16>, dim3(rows), dim3(HQ * 32), smem, stream, (bf16*)out, out_stride,
+                         out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, row_seq, row_pos,
+                         seq_slot, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, chunk, (const bf16*)gate,
+                         gate_stride, gate_col, gate_mode);
+}
+
+// scratch: n_seqs * HQ * splits * (DV + 2) floats
+KRK_API int krk_mixed_attention_single(void* out, int out_stride, int out_col, float out_scale, const void* proj, int stride,
+                                       int q_col, int HQ, int HKV, int D, int DV, const float* sink, const float* talk,
+                                       const int* seq_slot, const int* seq_start, const int* table, int width,
+                                       const void* k_cache, const void* v_cache, int n_seqs, float scale, int chunk,
+                                       int splits, float* scratch, const void* gate, int gate_stride, int gate_col,
+                                       int gate_mode, int dtype, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  if (HQ < 1 || HQ > 32 || HKV < 1 || HQ % HKV || DV > 32 * MIX_VPL || gate_mode > 1 || chunk < 0 || splits < 1 ||
+      n_seqs > 65535)
+    return -2;
+  const size_t smem = mixed_smem(HQ, D, talk != nullptr);
+  if (smem > 200 * 1024) return -2;
+  const int merge_blocks = (n_seqs * HQ + 3) / 4;
+  cudaError_t e;
+  if (dtype == KRK_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(mixed_attention_single_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(mixed_attention_single_kernel<float>, dim3(splits, n_seqs), dim3(HQ * 32), smem, stream, scratch,
+                   (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, seq_slot, seq_start, table, width,
+                   (const float*)k_cache, (const float*)v_cache, scale, chunk, splits);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_pdl(mixed_attention_merge_kernel<float>, dim3(merge_blocks), dim3(128), 0, stream, (float*)out,
+                           out_stride, out_col, out_scale, (const float*)scratch, HQ, DV, splits, n_seqs, (const float*)gate,
+                           gate_stride, gate_col, gate_mode);
+  }
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(mixed_attention_single_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  e = launch_pdl(mixed_attention_single_kernel<bf16>, dim3(splits, n_seqs), dim3(HQ * 32), smem, stream, scratch,
+                 (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, seq_slot, seq_start, table, width,
+                 (const bf16*)k_cache, (const bf16*)v_cache, scale, chunk, splits);
+  if (e != cudaSuccess) return (int)e;
+  return (int)launch_pdl(mixed_attention_merge_kernel<bf16>, dim3(merge_blocks), dim3(128), 0, stream, (bf16*)out, out_stride,
+                         out_col, out_scale, (const float*)scratch, HQ, DV, splits, n_seqs, (const bf16*)gate, gate_stride,
+                         gate_col, gate_mode);
+}
+
+KRK_API int krk_norm_sum(void* out, const void* y0, const void* y1, const void* y2, const void* y3, int n, const float* gain,
+                         int rows, int C, float eps, float scale, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (n < 1 || n > 4) return -2;
+  NormSumArgs a;
+  a.y[0] = y0; a.y[1] = y1; a.y[2] = y2; a.y[3] = y3;
+  a.gain = gain;
+  a.n = n;
+  const int threads = C >= 2048 ? 512 : (C >= 512 ? 256 : 128);
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(norm_sum_kernel<float>, dim3(rows), dim3(threads), 0, stream, (float*)out, a, C, eps, scale);
+  return (int)launch_pdl(norm_sum_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (bf16*)out, a, C, eps, scale);
+}
+
+KRK_API int krk_act_rows(void* out, const void* z, int z_stride, int rows, int I, int act, float pa, float pb, int dtype,
+                         cudaStream_t stream) {
+  if (rows == 0 || I == 0) return 0;
+  if (act != 0 && act != 1 && act != 4) return -2;
+  const long long total = (long long)rows * I;
+  const int blocks = (int)min((total + 255) / 256, (long long)148 * 16);
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(act_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, (const float*)z, z_stride,
+                           rows, I, act, pa, pb);
+  return (int)launch_pdl(act_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)out, (const bf16*)z, z_stride, rows,
+                         I, act, pa, pb);
+}

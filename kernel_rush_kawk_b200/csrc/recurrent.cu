@@ -23,21 +23,24 @@
 namespace {
 
 // out[s, r, c] = h[r, c] + (prev[r, c] - h[r, c]) * mu[s, c]; prev is the row before, or the
-// sequence's stored last row for the first row of its step.
+// sequence's stored last row for the first row of its step. With `store`, the thread that read element c of the
+// stored row then puts element c of the step's last row of that sequence in its place.
 template <typename T>
-__global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, int h_stride, const float* last_state,
+__global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, int h_stride, float* last_state,
                                    const float* __restrict__ mu, int n_mix, int C, int rows,
                                    const int* __restrict__ row_seq, const int* __restrict__ cu_q,
-                                   const int* __restrict__ seq_slot) {
+                                   const int* __restrict__ seq_slot, int store) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int r = blockIdx.x;
   const int seq = row_seq[r];
   const bool first = cu_q[seq] == r;
-  const float* last = last_state + (size_t)seq_slot[seq] * C;
+  float* last = last_state + (size_t)seq_slot[seq] * C;
+  const int last_row = cu_q[seq + 1] - 1;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     const float hv = to_float<T>(h[(size_t)r * h_stride + c]);
     const float pv = first ? last[c] : to_float<T>(h[(size_t)(r - 1) * h_stride + c]);
+    if (first && store) last[c] = to_float<T>(h[(size_t)last_row * h_stride + c]);
     const float d = pv - hv;
     for (int s = 0; s < n_mix; ++s)
       out[((size_t)s * rows + r) * C + c] = from_float<T>(hv + d * mu[(size_t)s * C + c]);
@@ -607,16 +610,16 @@ int pick_split(const ScanArgs& a, float* prep, float* o_scratch, int rows, cudaS
 
 }  // namespace
 
-KRK_API int krk_token_shift(void* out, const void* h, int h_stride, const float* last_state, const float* mu, int n_mix,
+KRK_API int krk_token_shift(void* out, const void* h, int h_stride, float* last_state, const float* mu, int n_mix,
                             int C, int rows, const int* row_seq, const int* cu_q, const int* seq_slot, int dtype,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int store) {
   if (rows == 0) return 0;
   const int threads = C >= 1024 ? 256 : 128;
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(token_shift_kernel<float>, dim3(rows), dim3(threads), 0, stream, (float*)out, (const float*)h,
-                           h_stride, last_state, mu, n_mix, C, rows, row_seq, cu_q, seq_slot);
+                           h_stride, last_state, mu, n_mix, C, rows, row_seq, cu_q, seq_slot, store);
   return (int)launch_pdl(token_shift_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (bf16*)out, (const bf16*)h,
-                         h_stride, last_state, mu, n_mix, C, rows, row_seq, cu_q, seq_slot);
+                         h_stride, last_state, mu, n_mix, C, rows, row_seq, cu_q, seq_slot, store);
 }
 
 KRK_API int krk_linear_recurrence(int rule, const void* r, int r_stride, const void* k, int k_stride, const void* v,

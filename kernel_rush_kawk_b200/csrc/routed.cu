@@ -8,6 +8,9 @@
 // kernel, one block per row, was measured for single-token steps and lost to the product kernel before it: 1.72
 // against 1.53 ms a step of one sequence at 64 experts of width 2,048.)
 //
+// krk_moe_route_groups: the same walk over other scores (sigmoid scores, a stored correction for the choice, groups of
+// experts of which only the best may be chosen); see moe_route_groups_kernel.
+//
 // Few rows (single-token steps): a (row, chosen expert) pair reads its expert's weights once.
 //   krk_moe_gate_up_pairs: act[pair, f] = a(Wg_e[f] . x_r) * (Wu_e[f] . x_r), a warp per f, lanes over K.
 //   krk_moe_down_pairs: out[r, c] = add[r, c] + sum_j weight[r, j] * (Wd_e(j)[c] . act[(r, j)]), a warp per c;
@@ -87,6 +90,94 @@ __global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ 
   if (has_gate && lane == 0) row_gate[row] = act_of(src[E], 2);
   __syncwarp();
   route_row(z, E, top, lane, experts + (size_t)row * top, weights + (size_t)row * top, over_all);
+}
+
+// The largest of z[0..n) over a warp (ties: the lower index).
+__device__ __forceinline__ void warp_argmax(const float* z, int n, int lane, float* best_out, int* best_e_out) {
+  float best = -INFINITY;
+  int best_e = 0x7fffffff;
+  for (int e = lane; e < n; e += 32) {
+    const float v = z[e];
+    if (v > best) { best = v; best_e = e; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+    if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+  }
+  *best_out = best;
+  *best_e_out = best_e;
+}
+
+// Sigmoid scores chosen within the best groups: s = sigmoid(logit); the choice goes by c = s + correction; the experts
+// are `groups` equal runs of neighbours, a group's score is the sum of its two largest c (its one c where a group has one
+// expert), only the `keep` best groups' experts can be chosen; the weights are the chosen s / (their sum + 1e-20) * scale.
+__global__ void moe_route_groups_kernel(int* __restrict__ experts, float* __restrict__ weights, float* __restrict__ row_gate,
+                                        const float* __restrict__ logits, const float* __restrict__ correction, int rows,
+                                        int E, int has_gate, int top, int groups, int keep, float scale) {
+  extern __shared__ float z_s[];  // [warps][2 E + 2 groups]
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * ROUTE_WARPS + warp;
+  if (row >= rows) return;
+  float* c = z_s + (size_t)warp * (2 * E + 2 * groups);
+  float* s = c + E;
+  float* gs = s + E;
+  int* kept = reinterpret_cast<int*>(gs + groups);
+  const float* src = logits + (size_t)row * (E + has_gate);
+  for (int e = lane; e < E; e += 32) {
+    const float v = act_of(src[e], 2);
+    s[e] = v;
+    c[e] = v + correction[e];
+  }
+  if (has_gate && lane == 0) row_gate[row] = act_of(src[E], 2);
+  __syncwarp();
+  if (keep < groups) {
+    const int size = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;  // the largest and the second largest
+      for (int e = g * size; e < (g + 1) * size; ++e) {
+        const float v = c[e];
+        if (v > a) { b = a; a = v; }
+        else if (v > b) b = v;
+      }
+      gs[g] = size > 1 ? a + b : a;
+      kept[g] = 0;
+    }
+    __syncwarp();
+    for (int j = 0; j < keep; ++j) {
+      float best;
+      int best_g;
+      warp_argmax(gs, groups, lane, &best, &best_g);
+      if (lane == 0) {
+        gs[best_g] = -INFINITY;
+        kept[best_g] = 1;
+      }
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!kept[e / size]) c[e] = -INFINITY;  // struck out, not zero: choice scores can be negative
+    __syncwarp();
+  }
+  float total = 0.f, mine = 0.f;
+  int mine_e = 0;
+  for (int j = 0; j < top; ++j) {
+    float best;
+    int best_e;
+    warp_argmax(c, E, lane, &best, &best_e);
+    const float v = s[best_e];
+    total += v;
+    if (lane == j) { mine = v; mine_e = best_e; }
+    __syncwarp();
+    if (lane == 0) c[best_e] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    experts[(size_t)row * top + lane] = mine_e;
+    weights[(size_t)row * top + lane] = mine / (total + 1e-20f) * scale;
+  }
 }
 
 constexpr int PAIR_WARPS = 8;
@@ -251,6 +342,19 @@ KRK_API int krk_moe_route(int* experts, float* weights, float* row_gate, const f
   if (smem > 48 * 1024) return -2;
   return (int)launch_pdl(moe_route_kernel, dim3((rows + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream,
                          experts, weights, row_gate, logits, bias, rows, E, has_gate, top, over_all);
+}
+
+KRK_API int krk_moe_route_groups(int* experts, float* weights, float* row_gate, const float* logits, const float* correction,
+                                 int rows, int E, int has_gate, int top, int groups, int keep, float scale,
+                                 cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (top < 1 || top > 32 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups ||
+      top > keep * (E / groups))
+    return -2;
+  const size_t smem = (size_t)ROUTE_WARPS * (2 * E + 2 * groups) * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+  return (int)launch_pdl(moe_route_groups_kernel, dim3((rows + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem,
+                         stream, experts, weights, row_gate, logits, correction, rows, E, has_gate, top, groups, keep, scale);
 }
 
 KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, const void* w, const int* experts, int rows,

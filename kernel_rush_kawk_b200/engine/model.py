@@ -60,9 +60,11 @@ class PartTree:
             built = [mixer_norm, mixer]
             ffn_norm = ffn = None
             if spec.feed_forward is not None:
-                ffn_norm = _build(spec.feed_forward_norm, parts_base.norm_class)
                 ffn = _build(spec.feed_forward, parts_base.feed_forward_class)
-                built += [ffn_norm, ffn]
+                built.append(ffn)
+                if spec.feed_forward_norm is not None:  # none: the arrangement feeds the mixer's norm to both
+                    ffn_norm = _build(spec.feed_forward_norm, parts_base.norm_class)
+                    built.append(ffn_norm)
             if self.position is not None and hasattr(mixer.part, "set_position"):
                 mixer.part.set_position(self.position.part)
             extra = () if spec.block_params is None else (dict(spec.block_params),)
@@ -109,12 +111,14 @@ class PartTree:
         return sorted(dims)
 
     def cache_needs(self) -> list:
+        """One entry per run of the schedule, then one for the embedding (None where it keeps nothing)."""
         needs = []
         for entry in self.plan.schedule:
             if entry.cache_from is not None:
                 needs.append(("from", entry.cache_from))
             else:
                 needs.append(self.layers[entry.layer][0].mixer.cache_need())
+        needs.append(self.embedding.part.cache_need())
         return needs
 
 
@@ -136,6 +140,7 @@ class Model:
         self.head = self.tree.head.part
         self.final_norm = self.tree.final_norm.part
         self.position = self.tree.position.part if self.tree.position is not None else None
+        self.embedding_keeps_state = self.embedding.cache_need() is not None
         self.blocks = [block for block, _ in self.tree.layers]
         self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
                               for part in (block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward)
@@ -151,7 +156,10 @@ class Model:
         [len(want_rows), vocab] (``want_rows``: int32 device tensor of row indices, or
         None for every row)."""
         ops = ctx.ops
-        x = self.embedding.forward(ctx)
+        if self.embedding_keeps_state:
+            x = self.embedding.forward(ctx, ctx.cache_view(len(self.plan.schedule)))
+        else:
+            x = self.embedding.forward(ctx)
         if self.position is not None:
             x = self.position.on_embeddings(ctx, x)
         stream = Stream(x)

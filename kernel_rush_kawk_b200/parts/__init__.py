@@ -10,8 +10,8 @@ from .rope import RotaryTable
 from .attention import GQAttention
 from .mlp import SwiGLU
 from .block import ParallelResidualBlock, PreNormBlock
-from .embedding import OutputHead, TokenEmbedding
-from .wide import GatedMLP, ScaledEmbedding, WideRMSNorm
+from .embedding import BigramEmbedding, OutputHead, TokenEmbedding
+from .wide import DenseMLP, GatedMLP, ScaledEmbedding, WideRMSNorm
 from .branches import Branch, ParallelMixer
 from .sink_attention import SinkWindowAttention
 from .recurrent import DeltaRule, TimeMixWKV
@@ -19,5 +19,6 @@ from .latent_attention import LatentAttention
 from .moe import RoutedExperts
 from .hyper import HyperRMSNorm
 from .ssm import Mamba2
+from .wrappers import NormedSum, TokenShifted
 
 __all__ = [n for n in dir() if not n.startswith("_")]

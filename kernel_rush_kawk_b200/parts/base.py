@@ -30,7 +30,7 @@ class TensorSpec:
     """Shape and role of one tensor a part owns.
 
     ``role`` decides dtype policy and random initialisation: "matrix" (compute
-    dtype, normal(0, std)), "gain" (a norm's weight: 1 + normal(0, std)), "table"
+    dtype, normal(0, std)), "gain" (a norm's weight: 1 + normal(0, std)), "mixing" (a square matrix: identity + normal(0, std)), "table"
     (an embedding: normal(0, std))."""
 
     shape: tuple[int, ...]
@@ -58,7 +58,7 @@ class KVNeed:
 @dataclass(frozen=True)
 class StateNeed:
     """Per-sequence state of fixed size, zeroed when a slot is handed out.
-    ``dtype`` is "compute" (the path's dtype) or "float32"."""
+    ``dtype`` is "compute" (the path's dtype), "float32" or "int32"."""
 
     shape: tuple[int, ...]
     dtype: str = "float32"
@@ -94,6 +94,11 @@ class Norm(Part):
 
 
 class Embedding(Part):
+    def cache_need(self):
+        """None, or a StateNeed for an embedding that depends on earlier tokens of the sequence (its
+        ``forward`` then gets the view of that storage as a second argument)."""
+        return None
+
     def forward(self, ctx):
         """The step's rows [rows, hidden] from ``ctx.batch.tokens``."""
         raise NotImplementedError

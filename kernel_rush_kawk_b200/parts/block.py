@@ -1,7 +1,7 @@
 """Block arrangements: how a layer's parts sit around the residual stream.
 
 "parallel_residual": x <- x + m * (Mixer(norm1(x)) + FeedForward(norm2(x))), both norms
-of the same x (one pass gives both), m a parameter of the arrangement; the two outputs
+of the same x (one pass gives both; a layer that names no second norm feeds norm1(x) to both), m a parameter of the arrangement; the two outputs
 stay pending with their multiplier and the next norm folds them in, in 32-bit.
 
 "prenorm" is the Qwen3 decoder layer, x += Mixer(norm(x)); x += FeedForward(norm(x))
@@ -45,6 +45,12 @@ class ParallelResidualBlock(Block):
             h1 = self.mixer_norm.forward(ctx, stream)
             stream.branch = self.mixer.forward(ctx, h1, cache)
             stream.scale = self.multiplier
+            return stream
+        if self.feed_forward_norm is None:  # one norm, read by both
+            h = self.mixer_norm.forward(ctx, stream)
+            a = self.mixer.forward(ctx, h, cache)
+            b = self.feed_forward.forward(ctx, h)
+            stream.branch, stream.branch2, stream.scale = a, b, self.multiplier
             return stream
         h1, h2 = self.mixer_norm.forward_pair(ctx, stream, self.feed_forward_norm)
         a = self.mixer.forward(ctx, h1, cache)

@@ -7,7 +7,7 @@ head is tied (engine/model.py:103-107,303). Logits leave in 32-bit.
 
 from __future__ import annotations
 
-from .base import Embedding, Head, TensorSpec, register_embedding, register_head
+from .base import Embedding, Head, StateNeed, TensorSpec, register_embedding, register_head
 
 
 class TokenEmbedding(Embedding):
@@ -27,6 +27,34 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx):
         return ctx.ops.embed(self.table, ctx.batch.tokens, ctx.batch.n_rows)
+
+
+class BigramEmbedding(Embedding):
+    """x[r] = table[id_r] + pairs[(id_prev * mul_prev + id_r * mul_cur) mod buckets], with the pair table's last row
+    (number ``buckets``) for a sequence's first token; the sum and the rows are 32-bit. The sequence's last token id
+    is kept as fixed-size state, so that a step may start anywhere. params: vocab, hidden, buckets, mul_prev, mul_cur."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.vocab = int(params["vocab"])
+        self.hidden = int(params["hidden"])
+        self.buckets = int(params["buckets"])
+        self.mul_prev = int(params["mul_prev"])
+        self.mul_cur = int(params["mul_cur"])
+        self.table = self.pairs = None
+
+    def tensor_specs(self):
+        return {"table": TensorSpec((self.vocab, self.hidden), "table"),
+                "pairs": TensorSpec((self.buckets + 1, self.hidden), "table")}
+
+    def cache_need(self):
+        return StateNeed((1,), "int32")
+
+    def bind(self, tensors, runtime):
+        self.table, self.pairs = tensors["table"], tensors["pairs"]
+
+    def forward(self, ctx, cache):
+        return ctx.ops.embed_bigram(self.table, self.pairs, cache.state, self.buckets, self.mul_prev, self.mul_cur, ctx.batch)
 
 
 class OutputHead(Head):
@@ -53,4 +81,5 @@ class OutputHead(Head):
 
 
 register_embedding("token_embedding", TokenEmbedding)
+register_embedding("bigram_embedding", BigramEmbedding)
 register_head("output_head", OutputHead)

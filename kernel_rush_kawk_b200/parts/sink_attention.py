@@ -24,6 +24,15 @@ Three options of the projections and the sink. ``bias``: q, k and v have biases 
 by a weight of the row's size ("q.norm"), and the k row likewise ("k.norm"), after the biases and before the
 rotation, in 32-bit. ``sink`` "zero": the extra term of the softmax's denominator is exp(0) for every head,
 p_j = exp(s_j) / (1 + sum exp(s_j)), and no tensor is read for it.
+
+Options of a second kind of this attention, which come with kernels of their own (a fused bias + norm + rotation +
+cache write, and an attention kernel whose block holds all heads of a row). ``qk_norm`` "head": every q head and
+every k head is divided by its own root mean square and multiplied by a weight of the head's size, shared by the
+heads ("q.norm", "k.norm" of ``dim`` elements), after the biases and before the rotation. ``rot_pairs``: the rotation
+pairs element 2i with element 2i + 1 instead of i with i + rot_dims/2. ``rot_factor``: every rotation frequency is
+divided by it. ``chunk``: a query at position p sees the keys of its own block of ``chunk`` positions only,
+(p // chunk) * chunk .. p, blocks counted from the sequence's first position. ``talk``: the heads' scaled scores of
+a (query, key) pair are mixed before the softmax, s'_h = sum_g T[h, g] s_g with a learned T ("talk", [heads, heads]).
 """
 
 from __future__ import annotations
@@ -37,8 +46,8 @@ from .branches import Branch
 class SinkWindowAttention(Branch):
     """params: hidden, heads, kv_heads, dim, vdim, scale, window (None or int), rot_dims, rot_base,
     value_norm (bool), sink (bool), eps, keep_first (int), gate (None, "head" or "element"),
-    value_mix (None, "first" or "blend"), value_mix_key, bias (bool), qk_norm (None or "row"); sink may
-    be "zero"."""
+    value_mix (None, "first" or "blend"), value_mix_key, bias (bool), qk_norm (None, "row" or "head"); sink may
+    be "zero"; rot_pairs (bool), rot_factor, chunk (None or int), talk (bool)."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -57,8 +66,14 @@ class SinkWindowAttention(Branch):
         self.has_sink = bool(p.get("sink", False)) and not self.zero_sink
         self.bias = bool(p.get("bias", False))
         self.qk_norm = p.get("qk_norm")
-        if self.qk_norm not in (None, "row"):
-            raise ValueError(f"qk_norm must be None or 'row', got {self.qk_norm!r}")
+        if self.qk_norm not in (None, "row", "head"):
+            raise ValueError(f"qk_norm must be None, 'row' or 'head', got {self.qk_norm!r}")
+        self.rot_pairs = bool(p.get("rot_pairs", False))
+        self.rot_factor = float(p.get("rot_factor", 1.0))
+        self.chunk = None if p.get("chunk") is None else int(p["chunk"])
+        self.talk = bool(p.get("talk", False))
+        #: the second kind of this attention (see the module text)
+        self._mixed = self.qk_norm == "head" or self.rot_pairs or self.chunk is not None or self.talk
         self.eps = float(p.get("eps", 0.0))
         self.keep_first = int(p.get("keep_first") or 0) if self.window is not None else 0
         self.gate = p.get("gate")
@@ -72,6 +87,10 @@ class SinkWindowAttention(Branch):
             raise ValueError(f"heads ({self.heads}) must be a multiple of kv_heads ({self.kv_heads})")
         if self.rot_dims % 2 or self.rot_dims > self.dim:
             raise ValueError(f"rot_dims ({self.rot_dims}) must be even and at most dim ({self.dim})")
+        if self._mixed and (self.window is not None or self.value_norm or self.value_mix or self.qk_norm == "row"
+                            or self.gate == "element" or (self.chunk is not None and self.chunk < 1)):
+            raise ValueError("per-head norms, pair rotation, blocks of keys and mixed scores come without a window, value "
+                             "norm, value blend, row norm or per-element gate")
 
     def tensor_specs(self):
         specs = {"q": TensorSpec((self.heads * self.dim, self.hidden)),
@@ -86,9 +105,13 @@ class SinkWindowAttention(Branch):
             specs.update({"q.b": TensorSpec((self.heads * self.dim,), "vector"),
                           "k.b": TensorSpec((self.kv_heads * self.dim,), "vector"),
                           "v.b": TensorSpec((self.kv_heads * self.vdim,), "vector")})
-        if self.qk_norm:
+        if self.qk_norm == "row":
             specs.update({"q.norm": TensorSpec((self.heads * self.dim,), "gain"),
                           "k.norm": TensorSpec((self.kv_heads * self.dim,), "gain")})
+        if self.qk_norm == "head":
+            specs.update({"q.norm": TensorSpec((self.dim,), "gain"), "k.norm": TensorSpec((self.dim,), "gain")})
+        if self.talk:
+            specs["talk"] = TensorSpec((self.heads, self.heads), "mixing")
         if self.value_mix:
             specs["vmix"] = TensorSpec((), "vector")  # the first layer of a blend stores one too and never reads it
         return specs
@@ -102,6 +125,8 @@ class SinkWindowAttention(Branch):
         return not (self.keep_first or self.gate or self.value_mix)
 
     def attention_head_dims(self):
+        if self._mixed:
+            return ()
         """Steps of many tokens in bfloat16 run on the tensor cores where key and value heads have one size that
         is a multiple of 16: that kernel is compiled per head size."""
         return (self.dim,) if self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
@@ -118,7 +143,8 @@ class SinkWindowAttention(Branch):
         # the few rotation frequencies come from the host in 64-bit, so that they depend on no device's pow()
         # and as two floats each (the float32 value, then what float32 leaves of the float64 value)
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
-        f = self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))
+        f = self.rot_base ** (-2.0 * i / max(self.rot_dims, 1)) / self.rot_factor
+        self.talk_w = tensors["talk"].float().contiguous() if self.talk else None
         hi = f.to(torch.float32)
         self.inv_freq = torch.cat([hi, (f - hi.double()).to(torch.float32)]).contiguous().to(runtime.device)
         self.bind_standalone()
@@ -134,6 +160,13 @@ class SinkWindowAttention(Branch):
         k_col = self.heads * self.dim
         v_col = k_col + self.kv_heads * self.dim
         value_eps = self.eps if self.value_norm else None
+        if self._mixed:
+            ops.bias_norm_rotate_write(proj, 0, k_col, v_col, self.heads, self.kv_heads, self.dim, self.vdim, self.qkv_bias,
+                                       self.qk_gain, self.eps, self.inv_freq, self.rot_dims, self.rot_pairs, ctx.batch, cache)
+            gate = (v_col + self.kv_heads * self.vdim, self.gate) if self.gate else None
+            ops.mixed_attention(proj, 0, self.heads, self.dim, self.vdim, self.sink, self.talk_w, self.scale, self.chunk,
+                                ctx.batch, cache, out, col0, scale, gate=gate)
+            return
         if self.bias or self.qk_norm:  # biases onto q, k, v; q and k rows divided by their root mean square
             ops.bias_row_norm(proj, (0, k_col, v_col, v_col + self.kv_heads * self.vdim), self.qkv_bias, self.qk_gain,
                               self.eps)

@@ -13,6 +13,9 @@
   the activation and the product are computed in float32 and rounded once.
   ``swish_clamped`` (parameters ``limit`` L and ``slope`` a) clamps both inputs first,
   g' = min(g, L), u' = clamp(u, -L, L), and gives g' sigmoid(a g') (u' + 1).
+* ``DenseMLP``: down(act(up h)) without a gate. ``xielu`` has two learned numbers (p, q) in a tensor of its own:
+  z > 0: softplus(p) z^2 + z/2; z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2. ``gelu_tanh`` and ``silu``
+  have none.
 """
 
 from __future__ import annotations
@@ -132,6 +135,37 @@ class GatedMLP(FeedForward):
         return ctx.ops.linear(act, self.w_down)
 
 
+class DenseMLP(FeedForward):
+    """params: hidden, intermediate, activation ("xielu", "gelu_tanh" or "silu"). Tensors: up, down and, for
+    xielu, act [2]."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.hidden = int(params["hidden"])
+        self.intermediate = int(params["intermediate"])
+        self.activation = str(params.get("activation", "xielu"))
+        if self.activation not in ("xielu", "gelu_tanh", "silu"):
+            raise ValueError(f"unknown activation '{self.activation}' for a dense feed-forward")
+        self.w_up = self.w_down = None
+        self.act_params = (0.0, 0.0)
+
+    def tensor_specs(self):
+        specs = {"up": TensorSpec((self.intermediate, self.hidden)), "down": TensorSpec((self.hidden, self.intermediate))}
+        if self.activation == "xielu":
+            specs["act"] = TensorSpec((2,), "vector")
+        return specs
+
+    def bind(self, tensors, runtime):
+        self.w_up, self.w_down = tensors["up"].contiguous(), tensors["down"].contiguous()
+        if self.activation == "xielu":  # the two slopes, once, in 64-bit: softplus(p) and 1/2 + softplus(q)
+            p, q = torch.nn.functional.softplus(tensors["act"].double().cpu()).tolist()
+            self.act_params = (p, 0.5 + q)
+
+    def forward(self, ctx, h):
+        return ctx.ops.linear(ctx.ops.act_rows(ctx.ops.linear(h, self.w_up), self.activation, self.act_params), self.w_down)
+
+
 register_embedding("scaled_embedding", ScaledEmbedding)
+register_feed_forward("dense_mlp", DenseMLP)
 register_norm("rmsnorm_wide", WideRMSNorm)
 register_feed_forward("gated_mlp", GatedMLP)

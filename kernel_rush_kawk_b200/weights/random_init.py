@@ -132,6 +132,9 @@ def random_tensor(name: str, spec, seed: int, std: float, device="cpu", gain_std
     z = standard_normals(n, _key_of(name, seed), device)
     if spec.role == "gain":
         z = z * (std if gain_std is None else gain_std) + 1.0
+    elif spec.role == "mixing" and len(shape) == 2 and shape[0] == shape[1]:
+        # a square matrix that mixes like things (heads, say): the identity plus noise
+        z = z * std + torch.eye(shape[0], dtype=z.dtype, device=z.device).reshape(-1)
     else:
         z = z * std
     return z.float().to(torch.bfloat16).view(shape)

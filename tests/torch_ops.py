@@ -228,16 +228,139 @@ class _WideOps:
         out[:, out_col:out_col + heads * n] = y.to(out.dtype)
         return out
 
-    def moe_route(self, x, w, b, top, gate_row=False, over_all=False):
+    def moe_route(self, x, w, b, top, gate_row=False, over_all=False, sigmoid_groups=None):
         z = x.float() @ w.float().t()
         row_gate = torch.sigmoid(z[:, -1]) if gate_row else None
         z = z[:, :-1] if gate_row else z
+        if sigmoid_groups is not None:
+            return (*self._route_sigmoid_groups(z, top, *sigmoid_groups), row_gate)
         if b is not None:
             z = z + b.float()
         best = torch.topk(z, top, dim=-1)  # ties are not exercised: equal logits do not occur with random weights
         if over_all:
             return best.indices.to(torch.int32), torch.softmax(z, dim=-1).gather(1, best.indices), row_gate
         return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1), row_gate
+
+    # -- pair-hash embedding, per-head norms with pair rotation, attention with mixed head scores over blocks
+    # of keys, norms of several outputs summed, plain activations, sigmoid routing within groups --------------
+    def embed_bigram(self, table, pairs, state, buckets, mul_prev, mul_cur, batch):
+        tok = batch.tokens.long()
+        prev = torch.empty_like(tok)
+        prev[1:] = tok[:-1]
+        first = torch.zeros(tok.shape[0], dtype=torch.bool)
+        row0 = 0
+        for slot, start, n in zip(batch.slots, batch.starts, batch.q_lens):
+            prev[row0] = state[slot, 0]
+            first[row0] = start == 0
+            state[slot, 0] = tok[row0 + n - 1]
+            row0 += n
+        row = (prev * mul_prev + tok * mul_cur) % buckets
+        row = torch.where(first, torch.full_like(row, buckets), row)
+        return table[tok].float() + pairs[row].float()
+
+    def bias_norm_rotate_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, bias, qk_gain, eps, inv_freq,
+                               rot_dims, pairs, batch, cache):
+        rows = proj.shape[0]
+        pos = batch.row_pos.long()
+        half = rot_dims // 2
+        end = v_col + kv_heads * vdim
+        x = proj[:, q_col:end].float()
+        if bias is not None:
+            x = x + bias
+        q = x[:, :k_col - q_col].reshape(rows, heads, dim)
+        k = x[:, k_col - q_col:v_col - q_col].reshape(rows, kv_heads, dim)
+        v = x[:, v_col - q_col:].reshape(rows, kv_heads, vdim)
+        if qk_gain is not None:
+            q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps) * qk_gain[:dim]
+            k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps) * qk_gain[dim:]
+
+        def rotate(t):
+            if not half:
+                return t
+            f = inv_freq[:half].double() + inv_freq[half:].double()
+            a = pos.double()[:, None] * f[None, :]
+            c, sn = torch.cos(a).float()[:, None, :], torch.sin(a).float()[:, None, :]
+            if pairs:
+                u, w = t[..., 0:rot_dims:2], t[..., 1:rot_dims:2]
+                turned = torch.stack([u * c - w * sn, w * c + u * sn], dim=-1).reshape(t.shape[0], t.shape[1], rot_dims)
+            else:
+                u, w = t[..., :half], t[..., half:rot_dims]
+                turned = torch.cat([u * c - w * sn, w * c + u * sn], dim=-1)
+            return torch.cat([turned, t[..., rot_dims:]], dim=-1)
+
+        proj[:, q_col:q_col + heads * dim] = rotate(q).reshape(rows, heads * dim).to(proj.dtype)
+        slot = batch.seq_slot.long()[batch.row_seq.long()]
+        page = cache.table.long()[slot, _entry(cache, pos)]
+        cache.k[page, :, pos % PAGE] = rotate(k).to(proj.dtype)
+        cache.v[page, :, pos % PAGE] = v.to(proj.dtype)
+
+    def mixed_attention(self, proj, q_col, heads, dim, vdim, sink, talk, scale, chunk, batch, cache, out, out_col, out_scale,
+                        gate=None):
+        rows = proj.shape[0]
+        G = heads // cache.kv_heads
+        q = proj[:, q_col:q_col + heads * dim].reshape(rows, heads, dim).float()
+        res = torch.empty((rows, heads, vdim), dtype=torch.float32, device=proj.device)
+        table = cache.table.long()
+        row0 = 0
+        for slot, start, n in zip(batch.slots, batch.starts, batch.q_lens):
+            total = start + n
+            lo = (start // chunk) * chunk if chunk else 0
+            positions = torch.arange(lo, total, device=proj.device)
+            pages = table[slot, _entry(cache, positions)]
+            k = cache.k[pages, :, positions % PAGE].float()  # [keys, kv heads, dim]
+            v = cache.v[pages, :, positions % PAGE].float()
+            qpos = torch.arange(start, total, device=proj.device)
+            visible = positions[None, :] <= qpos[:, None]
+            if chunk:
+                visible &= (positions[None, :] // chunk) == (qpos[:, None] // chunk)
+            kh = torch.arange(heads) // G
+            s = torch.einsum("qhd,khd->hqk", q[row0:row0 + n], k[:, kh]) * scale
+            if talk is not None:
+                s = torch.einsum("hg,gqk->hqk", talk.float(), s)
+            s = s.masked_fill(~visible[None], float("-inf"))
+            m = s.max(dim=-1, keepdim=True).values
+            extra = 0.0
+            if sink is not None:
+                m = torch.maximum(m, sink.float()[:, None, None])
+                extra = torch.exp(sink.float()[:, None, None] - m)
+            p = torch.exp(s - m)
+            o = torch.einsum("hqk,khd->hqd", p, v[:, kh]) / (p.sum(dim=-1, keepdim=True) + extra)
+            res[row0:row0 + n] = o.transpose(0, 1)
+            row0 += n
+        if gate is not None:
+            col, mode = gate
+            width = heads * (vdim if mode == "element" else 1)
+            res = res * torch.sigmoid(proj[:, col:col + width].float()).reshape(rows, heads, -1)
+        out[:, out_col:out_col + heads * vdim] = (res * out_scale).to(out.dtype).view(rows, heads * vdim)
+
+    def norm_sum(self, outs, gains, eps, scale):
+        total = 0.0
+        for y, g in zip(outs, gains):
+            yf = y.float()
+            total = total + yf * torch.rsqrt((yf * yf).mean(dim=-1, keepdim=True) + eps) * g.float()
+        return (total * scale).to(outs[0].dtype)
+
+    def act_rows(self, z, activation, params=(0.0, 0.0)):
+        zf = z.float()
+        if activation == "xielu":
+            a, b = params
+            out = torch.where(zf > 0, a * zf * zf + 0.5 * zf, b * (torch.expm1(zf) - zf) + 0.5 * zf)
+        else:
+            out = _act(zf, activation)
+        return out.to(z.dtype)
+
+    def _route_sigmoid_groups(self, z, top, correction, groups, keep, scale):
+        rows, E = z.shape
+        s = torch.sigmoid(z)
+        c = s + correction.float()
+        size = E // groups
+        score = c.view(rows, groups, size).topk(min(2, size), dim=-1).values.sum(dim=-1)
+        best = score.topk(keep, dim=-1).indices
+        allowed = torch.zeros((rows, groups), dtype=torch.bool).scatter_(1, best, True)
+        c = c.masked_fill(~allowed.repeat_interleave(size, dim=1), float("-inf"))
+        idx = c.topk(top, dim=-1).indices
+        w = s.gather(1, idx)
+        return idx.to(torch.int32), w / (w.sum(dim=-1, keepdim=True) + 1e-20) * scale
 
     # -- hyper-connections, the state-space mixer, biases and row norms of attention --------------------
     def hyper_rmsnorm(self, x, branch, fold, read, gain, offset, eps, x_new, out_dtype):
@@ -394,13 +517,15 @@ class _WideOps:
         self.sink_attention(proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale)
         return True
 
-    def token_shift(self, h, last_state, mu, batch):
+    def token_shift(self, h, last_state, mu, batch, store=False):
         hf = h.float()
         prev = torch.empty_like(hf)
         prev[1:] = hf[:-1]
         row0 = 0
         for slot, n in zip(batch.slots, batch.q_lens):
             prev[row0] = last_state[slot]
+            if store:
+                last_state[slot] = hf[row0 + n - 1]
             row0 += n
         return (hf[None] + (prev - hf)[None] * mu.float()[:, None, :]).to(h.dtype)
 
