@@ -37,6 +37,12 @@ feed-forwards) at two sizes beside its closest existing model, the Taredra hybri
 feed-forward, heads and layer count (recurrent layers beside attention, a 32-bit stream), and beside the Qwen3
 decoder of that size.
 
+``--only design_fogizen`` measures the Fogizen decoder (attention over blocks of keys with mixed head scores, per-head
+norms and a sink beside RWKV-style time mixing, a token-shifted mixer input, a pair-hash embedding, dense xIELU
+and routed feed-forwards chosen by sigmoid scores within groups) at two sizes beside its closest existing model,
+the Taredra hybrid decoder of equal width, feed-forward, heads and layer count, and beside the Qwen3 decoder of
+that size.
+
 ``--only workload_8b`` and ``--only workload_14b`` run the baseline's two larger
 configurations (Qwen3-8B sizes: 8 prompts of 256 to 2,048 tokens, 128 greedy steps;
 Qwen3-14B sizes: 16 prompts of 512 to 4,096 tokens, 128 steps at temperature 0.7)
@@ -216,20 +222,25 @@ DESIGN_SIZES = {
                    "head_dim": 128, "vocab_size": 32768},
     "zadunex_4b": {"hidden_size": 2560, "intermediate_size": 9728, "num_attention_heads": 32, "num_key_value_heads": 8,
                    "head_dim": 128, "vocab_size": 32768},
+    "fogizen_1b": {"hidden_size": 1536, "intermediate_size": 6144, "num_attention_heads": 12, "num_key_value_heads": 4,
+                   "head_dim": 128, "vocab_size": 32768},
+    "fogizen_4b": {"hidden_size": 2560, "intermediate_size": 9728, "num_attention_heads": 32, "num_key_value_heads": 8,
+                   "head_dim": 128, "vocab_size": 151936},
 }
 #: a design's closest existing model of equal size, measured beside it as well (preset -> preset)
-DESIGN_NEIGHBOURS = {"zadunex_1b": "taredra_1b", "zadunex_4b": "taredra_4b"}
+DESIGN_NEIGHBOURS = {"zadunex_1b": "taredra_1b", "zadunex_4b": "taredra_4b", "fogizen_1b": "taredra_1b",
+                     "fogizen_4b": "taredra_4b"}
 KERNEL_FAMILIES = {
     "product": ("_skinny", "_library_gemm", "_gemm_nt", "gemm_tcgen05"),
-    "norm": ("rmsnorm", "add_rmsnorm", "rmsnorm_wide", "hyper_rmsnorm"),
-    "activation": ("swiglu", "gated_act"),
+    "norm": ("rmsnorm", "add_rmsnorm", "rmsnorm_wide", "hyper_rmsnorm", "norm_sum"),
+    "activation": ("swiglu", "gated_act", "act_rows"),
     "attention": ("rope_attention", "rotate_norm_write", "sink_attention", "latent_norm_write", "head_linear",
-                  "bias_row_norm"),
+                  "bias_row_norm", "bias_norm_rotate_write", "mixed_attention"),
     "recurrence": ("token_shift", "linear_recurrence", "causal_conv_silu", "ssd_scan", "gated_group_norm"),
     # routing and the routed experts; for steps of many tokens this holds the experts' dense products too, which
     # the product family counts as well
     "experts": ("moe_route", "moe_experts"),
-    "embedding": ("embed", "embed_scaled", "gather_rows"),
+    "embedding": ("embed", "embed_scaled", "embed_bigram", "gather_rows"),
 }
 
 
@@ -654,7 +665,7 @@ def main() -> int:
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64",
                                                   "workload_8b", "workload_14b", "design_taredra", "design_disorax",
-                                                  "design_zadunex"],
+                                                  "design_zadunex", "design_fogizen"],
                    help="run one piece only (for profiling), or one of the baseline's larger configurations end to end")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()
