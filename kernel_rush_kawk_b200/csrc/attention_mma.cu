@@ -446,6 +446,218 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
 }
 
 // ---------------------------------------------------------------------------------
+// Attention whose heads' scores are mixed before the softmax, over the keys of the query's own block of
+// `chunk` positions (0: all earlier keys), for steps of many tokens. 16 consecutive tokens of one sequence are
+// served by one block with a warp per query head or, where the heads are too many for one block's registers and
+// shared memory, by a cluster of 2, 4 or 8 blocks that split the heads and read one another's scores through
+// distributed shared memory. Per page of keys: the K pages of all kv heads come to shared memory, warp h
+// forms its head's scaled scores S_h [16 x 64] on the tensor cores and leaves them in shared memory; after a
+// barrier the scores are mixed in float32, S'_h = sum_g talk[h, g] S_g (g ascending): in one block, warp h reads all
+// heads' scores at its own fragment positions; in a cluster, the tile's (query, key) pairs are dealt out over all
+// threads, each of which reads every head's score of its pair and writes every head's mixed score back in place,
+// so that a score crosses between blocks once per pair; the V pages replace the K pages meanwhile; masking, the online softmax (from the sink as
+// the starting state) and P.V with the weights as two bfloat16 halves follow as in sink_window_prefill_kernel.
+// ---------------------------------------------------------------------------------
+constexpr int MIX_MAX_HEADS = 32;  // heads whose scores of one (query, key) pair a thread holds while it mixes them
+constexpr int MIX_SP = 72;  // floats per row of the exchanged scores: 64 keys + 8, so that a half-warp's 8-byte accesses meet no bank twice
+
+template <int MAXW>
+__global__ void __launch_bounds__(MAXW * 32)
+mixed_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_scale, const bf16* __restrict__ q_base,
+                     int q_stride, int HQ, int HKV, const float* __restrict__ sink, const float* __restrict__ talk,
+                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                     const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
+                     int width, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, float scale,
+                     int chunk, const bf16* __restrict__ gate, int gate_stride, int gate_mode, int ncta, int max_kv) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int HPB = HQ / ncta;                       // heads of this block: one warp each
+  const int rank = ncta > 1 ? (int)cluster.block_rank() : 0;
+  bf16* kv = reinterpret_cast<bf16*>(smem_raw);                                       // [max_kv][64][KVP]: K, then V
+  float* sx = reinterpret_cast<float*>(smem_raw + (size_t)max_kv * TILE_ELEMS * sizeof(bf16));  // [HPB][16][MIX_SP]
+  const int HP = (HQ + 3) & ~3;
+  float* talk_t = sx + (size_t)HPB * 16 * MIX_SP;                                     // [HQ][HP]: talk transposed, [from][to]
+  float** plane = reinterpret_cast<float**>(talk_t + (size_t)HQ * HP);                // [HQ]: where head q's scores lie
+  const int seq = blockIdx.y;
+  const int tile = gridDim.x / ncta - 1 - blockIdx.x / ncta;  // the tiles with most keys first; a cluster shares a tile
+  const int q_len = seq_qlen[seq];
+  if (tile * 16 >= q_len) return;  // the whole cluster leaves
+  const int start = seq_start[seq], slot = seq_slot[seq], row0 = cu_q[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = rank * HPB + warp;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int G = HQ / HKV;
+  const int kh_lo = (rank * HPB) / G, kh_hi = (rank * HPB + HPB - 1) / G;  // the kv heads that this block's heads read
+  const int n_kv = kh_hi - kh_lo + 1;
+  const int kh = head / G - kh_lo;
+  const int n_threads = HPB * 32;
+  if (talk) {
+    for (int i = threadIdx.x; i < HQ * HP; i += n_threads) {
+      const int from = i / HP, to = i % HP;
+      talk_t[i] = to < HQ ? talk[(size_t)to * HQ + from] : 0.f;
+    }
+    // the scores of head q lie in the shared memory of the block that owns it
+    for (int q = threadIdx.x; q < HQ; q += n_threads)
+      plane[q] = (ncta > 1 ? cluster.map_shared_rank(sx, q / HPB) : sx) + (size_t)(q % HPB) * 16 * MIX_SP;
+  }
+
+  int pos[2], lo[2];
+  const bf16* qp[2];
+  bf16* op[2];
+  float gate_v[2];
+  float m[2], l[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int tok = tile * 16 + g + 8 * h;
+    const bool ok = tok < q_len;
+    pos[h] = ok ? start + tok : -1;
+    lo[h] = (ok && chunk > 0) ? (pos[h] / chunk) * chunk : 0;
+    qp[h] = ok ? q_base + (size_t)(row0 + tok) * q_stride + (size_t)head * D : nullptr;
+    op[h] = ok ? out + (size_t)(row0 + tok) * out_stride + (size_t)head * D : nullptr;
+    gate_v[h] = (ok && gate_mode == 1) ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(row0 + tok) * gate_stride + head]))) : 1.0f;
+    m[h] = sink ? sink[head] * LOG2E : -INFINITY;
+    l[h] = sink ? 1.f : 0.f;
+  }
+  uint32_t qf[KSTEPS][4];
+  load_q(qf, qp[0], qp[1], lane);
+  const int first_pos = start + tile * 16;
+  const int last_pos = start + min(q_len - 1, tile * 16 + 15);
+  const int j_lo = (chunk > 0 ? (first_pos / chunk) * chunk : 0) / KRK_PAGE;
+  const int j_hi = last_pos / KRK_PAGE;
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+
+  auto issue = [&](const bf16* cache, int j) {
+    const int page = table[(size_t)slot * width + j % width];
+    const bf16* src = cache + (size_t)page * page_stride + (size_t)kh_lo * KRK_PAGE * D;  // kv heads lie one after the other
+    const int pieces = n_kv * KRK_PAGE * (D / 8);
+    for (int i = threadIdx.x; i < pieces; i += n_threads) {
+      const int hk = i / (KRK_PAGE * (D / 8)), r = i % (KRK_PAGE * (D / 8));
+      const int key = r / (D / 8), ch = r % (D / 8);
+      cp_async_16(kv + (size_t)hk * TILE_ELEMS + kv_off(key, ch), src + ((size_t)hk * KRK_PAGE + key) * D + ch * 8);
+    }
+    cp_async_commit();
+  };
+  auto barrier_all = [&]() {  // every block that shares the tile
+    if (ncta > 1) cluster.sync();
+    else __syncthreads();
+  };
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  for (int j = j_lo; j <= j_hi; ++j) {
+    issue(k_cache, j);
+    cp_async_wait<0>();
+    __syncthreads();
+    float s[8][4];
+    qk_tile<8>(s, qf, kv + (size_t)kh * TILE_ELEMS, 0, lane);
+    const int key_base = j * KRK_PAGE;
+    if (talk) {
+      // raw scaled scores into shared memory; keys beyond the step's last token were never written: they count 0
+      float* mine = sx + (size_t)warp * 16 * MIX_SP;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int key = key_base + n * 8 + 2 * t4;
+        float2 a = make_float2(key <= last_pos ? s[n][0] * scale : 0.f, key + 1 <= last_pos ? s[n][1] * scale : 0.f);
+        float2 b = make_float2(key <= last_pos ? s[n][2] * scale : 0.f, key + 1 <= last_pos ? s[n][3] * scale : 0.f);
+        *reinterpret_cast<float2*>(mine + (size_t)g * MIX_SP + n * 8 + 2 * t4) = a;
+        *reinterpret_cast<float2*>(mine + (size_t)(g + 8) * MIX_SP + n * 8 + 2 * t4) = b;
+      }
+      barrier_all();  // every head's scores are there, and the K pages are done with
+    } else {
+      __syncthreads();
+    }
+    issue(v_cache, j);
+    if (talk && ncta == 1) {
+      // one block holds every head: warp h reads all heads' scores at its own fragment positions
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+      for (int q = 0; q < HQ; ++q) {
+        const float t = talk_t[(size_t)q * HP + warp];
+        const float* theirs = sx + (size_t)q * 16 * MIX_SP;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const float2 a = *reinterpret_cast<const float2*>(theirs + (size_t)g * MIX_SP + n * 8 + 2 * t4);
+          const float2 b = *reinterpret_cast<const float2*>(theirs + (size_t)(g + 8) * MIX_SP + n * 8 + 2 * t4);
+          s[n][0] += t * a.x;
+          s[n][1] += t * a.y;
+          s[n][2] += t * b.x;
+          s[n][3] += t * b.y;
+        }
+      }
+    } else if (talk) {
+      // The 16 x 64 (query, key) pairs of the tile are dealt out over all threads of the blocks that share it. A
+      // thread reads every head's score of its pair, forms every head's mixed score from them (from ascending) and
+      // puts it back in the same places: each score crosses between the blocks once per pair, not once per pair
+      // and head.
+      for (int p = rank * n_threads + threadIdx.x; p < 16 * KRK_PAGE; p += ncta * n_threads) {
+        const int off = (p / KRK_PAGE) * MIX_SP + p % KRK_PAGE;
+        float sv[MIX_MAX_HEADS];
+#pragma unroll
+        for (int q = 0; q < MIX_MAX_HEADS; ++q) sv[q] = q < HQ ? plane[q][off] : 0.f;
+        for (int to = 0; to < HQ; to += 4) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < MIX_MAX_HEADS; ++q) {
+            if (q < HQ) {
+              const float4 t = *reinterpret_cast<const float4*>(talk_t + (size_t)q * HP + to);
+              acc.x += t.x * sv[q];
+              acc.y += t.y * sv[q];
+              acc.z += t.z * sv[q];
+              acc.w += t.w * sv[q];
+            }
+          }
+          plane[to][off] = acc.x;
+          if (to + 1 < HQ) plane[to + 1][off] = acc.y;
+          if (to + 2 < HQ) plane[to + 2][off] = acc.z;
+          if (to + 3 < HQ) plane[to + 3][off] = acc.w;
+        }
+      }
+      cluster.sync();  // every pair is mixed
+      const float* mine = sx + (size_t)warp * 16 * MIX_SP;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const float2 a = *reinterpret_cast<const float2*>(mine + (size_t)g * MIX_SP + n * 8 + 2 * t4);
+        const float2 b = *reinterpret_cast<const float2*>(mine + (size_t)(g + 8) * MIX_SP + n * 8 + 2 * t4);
+        s[n][0] = a.x;
+        s[n][1] = a.y;
+        s[n][2] = b.x;
+        s[n][3] = b.y;
+      }
+    }
+    const float unit = talk ? LOG2E : scale * LOG2E;
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = key_base + n * 8 + 2 * t4 + (c & 1);
+        const int h = c >> 1;
+        s[n][c] = (key <= pos[h] && key >= lo[h]) ? s[n][c] * unit : -INFINITY;
+      }
+    softmax_update<8>(s, m, l, o);
+    cp_async_wait<0>();
+    __syncthreads();  // the V pages are there
+    pv_tile_wide<8>(o, s, kv + (size_t)kh * TILE_ELEMS, 0, lane);
+    __syncthreads();  // before the next K pages overwrite the V pages (and, in one block, the next scores these)
+  }
+  if (talk && ncta > 1) cluster.sync();  // no block leaves while another may still touch its shared memory
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!op[h]) continue;
+    const float inv = out_scale / l[h] * gate_v[h];
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n)
+      *reinterpret_cast<uint32_t*>(op[h] + n * 8 + 2 * t4) = pack_bf16x2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // One token per sequence. Block = (key split, kv head x row tile, sequence). The block
 // brings whole pages to shared memory; warp w works on keys 16w..16w+15 of each page
 // with running statistics of its own; the four warps merge at the end and the block
@@ -1419,6 +1631,62 @@ KRK_API int krk_sink_window_prefill(void* out, int out_stride, float out_scale, 
       (bf16*)out, out_stride, out_scale, (const bf16*)q_base, q_stride, HQ, HKV, sink, seq_slot, seq_start, seq_qlen,
       cu_q, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window, keep_first, keep_pages,
       (const bf16*)gate, gate_stride, gate_mode);
+  KRK_CHECK_LAUNCH();
+  return 0;
+}
+
+// Attention with mixed head scores over blocks of keys, for steps of many tokens (see mixed_prefill_kernel). q_base,
+// out and gate point at the first query / output / gate column of the wider rows (strides in elements; out and q even).
+// -2: a shape this kernel does not take (the heads do not split evenly over 1, 2, 4 or 8 blocks of at most 16 warps, 12
+// for heads of more than 64 elements, whose pages fit the shared memory).
+KRK_API int krk_mixed_prefill(void* out, int out_stride, float out_scale, const void* q_base, int q_stride, int HQ, int HKV,
+                              const float* sink, const float* talk, const int* seq_slot, const int* seq_start,
+                              const int* seq_qlen, const int* cu_q, const int* table, int width, const void* k_cache,
+                              const void* v_cache, int n_seqs, int max_q_len, float scale, int chunk, const void* gate,
+                              int gate_stride, int gate_mode, cudaStream_t stream) {
+  if (n_seqs == 0 || max_q_len == 0) return 0;
+  if (HQ < 1 || HQ > MIX_MAX_HEADS || HKV < 1 || HQ % HKV || gate_mode > 1 || chunk < 0 || n_seqs > 65535) return -2;
+  if ((out_stride & 1) || (q_stride & 1) || ((uintptr_t)out & 3) || ((uintptr_t)q_base & 3)) return -2;
+  const int most = D > 64 ? 12 : 16;  // warps whose accumulators fit a block's registers
+  const int G = HQ / HKV;
+  int ncta = 0, max_kv = 0;
+  size_t smem = 0;
+  for (int c = 1; c <= 8 && !ncta; c *= 2) {
+    if (HQ % c || HQ / c > most || (c > 1 && !talk)) continue;
+    const int hpb = HQ / c;
+    max_kv = 0;
+    for (int r = 0; r < c; ++r) max_kv = max(max_kv, (r * hpb + hpb - 1) / G - (r * hpb) / G + 1);
+    smem = (size_t)max_kv * TILE_ELEMS * sizeof(bf16) +
+           ((size_t)hpb * 16 * MIX_SP + (size_t)HQ * ((HQ + 3) & ~3)) * sizeof(float) + (size_t)HQ * sizeof(float*);
+    if (smem <= 220 * 1024) ncta = c;
+  }
+  if (!ncta) return -2;
+  const int hpb = HQ / ncta;
+  const long long tiles = (max_q_len + 15) / 16;
+  if (tiles * ncta > 0x7fffffffLL) return -3;
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * ncta), n_seqs);
+    cfg.blockDim = dim3(hpb * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ncta;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, (bf16*)out, out_stride, out_scale, (const bf16*)q_base, q_stride, HQ, HKV, sink, talk,
+                              seq_slot, seq_start, seq_qlen, cu_q, table, width, (const bf16*)k_cache, (const bf16*)v_cache,
+                              scale, chunk, (const bf16*)gate, gate_stride, gate_mode, ncta, max_kv);
+  };
+  cudaError_t e;
+  if (hpb <= 8) e = launch(mixed_prefill_kernel<8>);
+  else if (hpb <= 12) e = launch(mixed_prefill_kernel<12>);
+  else e = launch(mixed_prefill_kernel<16>);
+  if (e != cudaSuccess) return (int)e;
   KRK_CHECK_LAUNCH();
   return 0;
 }

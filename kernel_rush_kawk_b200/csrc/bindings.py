@@ -103,6 +103,8 @@ _ATTN_SIGNATURES = {
                               c_int, _P],
     "krk_sink_window_prefill": [_P, c_int, c_float, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
                                 c_int, c_float, c_int, c_int, c_int, _P, c_int, c_int, _P],
+    "krk_mixed_prefill": [_P, c_int, c_float, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
+                          c_int, c_float, c_int, _P, c_int, c_int, _P],
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
@@ -872,6 +874,17 @@ class Kernels:
                 ptr, stride, g_col, g_mode, _code(proj.dtype), self._stream()), "single-token attention with mixed scores")
             self.launches += 1
             return
+        if (proj.dtype == torch.bfloat16 and dim == vdim and dim in self.attn and hasattr(self.attn[dim], "krk_mixed_prefill")):
+            # many tokens per sequence in bfloat16: scores and P.V on the tensor cores (compiled per head size)
+            esz = proj.element_size()
+            rc = self.attn[dim].krk_mixed_prefill(
+                optr + out_col * esz, ostride, float(out_scale), ptr + q_col * esz, stride, heads, cache.kv_heads, _ptr(sink),
+                _ptr(talk), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(),
+                batch.cu_q.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
+                batch.n_seqs, batch.max_q_len, float(scale), chunk, ptr + g_col * esz, stride, g_mode, self._stream())
+            if rc != -2:  # -2: a shape it does not take; the general kernel does
+                self._ok(rc, "tensor-core attention with mixed scores")
+                return
         self._ok(self.mix.krk_mixed_attention(
             optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),
             _ptr(talk), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(),

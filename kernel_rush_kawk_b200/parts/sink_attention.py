@@ -126,7 +126,7 @@ class SinkWindowAttention(Branch):
 
     def attention_head_dims(self):
         if self._mixed:
-            return ()
+            return (self.dim,) if self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
         """Steps of many tokens in bfloat16 run on the tensor cores where key and value heads have one size that
         is a multiple of 16: that kernel is compiled per head size."""
         return (self.dim,) if self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()

@@ -24,11 +24,12 @@ def folders(tmp_path_factory):
     return {name: write_folder(root / name, name) for name in CONFIGS}
 
 
-def runtime(dtype):
+def runtime(dtype, head_dims=()):
+    """``head_dims``: the head sizes whose tensor-core attention libraries the test's steps of many tokens may use."""
     from kernel_rush_kawk_b200.csrc import load_kernels
     from kernel_rush_kawk_b200.engine.model import Runtime
 
-    return Runtime(torch.device("cuda:0"), dtype, load_kernels(()))
+    return Runtime(torch.device("cuda:0"), dtype, load_kernels(tuple(head_dims)))
 
 
 def rand(shape, seed, scale=1.0):
@@ -179,8 +180,9 @@ def left_part(shape, dtype, rt, seed=70):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", LEFT_SHAPES)
 def test_attention_with_mixed_scores_whole_in_pieces_and_token_by_token(dtype, shape):
-    rt = runtime(dtype)
+    rt = runtime(dtype, (shape[3],) if shape[3] == shape[4] and shape[3] % 16 == 0 else ())
     part, ref, m = left_part(shape, dtype, rt)
+    assert part.attention_head_dims() == ((shape[3],) if shape[3] == shape[4] and shape[3] % 16 == 0 else ())
     T = 150
     h = rand((T, shape[0]), 5, 1.0).to(dtype)
     want = plain.left_branch(h.double(), ref, "", m, 1e-5, torch.arange(T))
@@ -190,14 +192,16 @@ def test_attention_with_mixed_scores_whole_in_pieces_and_token_by_token(dtype, s
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, kv, dim, vdim, block", [(4, 2, 16, 8, 50), (3, 1, 8, 40, 64), (6, 6, 32, 32, 200), (2, 1, 16, 16, None)])
+@pytest.mark.parametrize("heads, kv, dim, vdim, block", [(4, 2, 16, 8, 50), (3, 1, 8, 40, 64), (6, 6, 32, 32, 200), (2, 1, 32, 32, None),
+                                                          (12, 4, 64, 64, 100), (24, 6, 32, 32, 80)])
 def test_a_planted_key_shows_just_inside_a_block_and_not_just_outside(dtype, heads, kv, dim, vdim, block):
     """One key is made to stand out for a query: as the block's first key it takes the whole softmax, as the last key
-    of the block before it must not be seen at all. Prompts and single tokens, page borders, a far key without blocks."""
+    of the block before it must not be seen at all. Prompts and single tokens, page borders, a far key without blocks.
+    (Twenty-four heads: in bfloat16 two thread blocks share a tile's heads and read one another's scores.)"""
     from kernel_rush_kawk_b200.cache import SequenceCache
     from kernel_rush_kawk_b200.parts import KVNeed
 
-    rt = runtime(dtype)
+    rt = runtime(dtype, (dim,) if dim == vdim and dim % 16 == 0 else ())  # bfloat16 prompts then take the tensor cores
     T = 330
     q = rand((T, heads, dim), 1)
     k = rand((T, kv, dim), 2)
