@@ -348,46 +348,75 @@ struct NormSumArgs {
   int n;
 };
 
-template <typename T>
+// V elements at a time (8 bfloat16 or 4 float32: 16 bytes); the row's inputs are held in shared memory between the
+// sums of squares and the weighted sum, so that global memory is read once.
+template <typename T, int V>
 __global__ void norm_sum_kernel(T* __restrict__ out, NormSumArgs a, int C, float eps, float scale) {
+  extern __shared__ __align__(16) float rows_s[];  // [n][C]
   __shared__ float scratch[32];
   grid_launch_dependents();
   grid_dependency_wait();
   const size_t row = blockIdx.x;
-  float rstd[4];
-  for (int b = 0; b < a.n; ++b) {
-    const T* y = reinterpret_cast<const T*>(a.y[b]) + row * C;
-    float sq = 0.f;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      const float v = to_float<T>(y[c]);
-      sq += v * v;
+  float sq[4] = {0.f, 0.f, 0.f, 0.f}, rstd[4];
+  // all inputs' pieces are requested before any sum is formed
+  for (int c = V * threadIdx.x; c < C; c += V * blockDim.x) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      if (b < a.n) {
+        __align__(16) T raw[V];
+        const T* y = reinterpret_cast<const T*>(a.y[b]) + row * C;
+        if (V == 1) raw[0] = y[c];
+        else *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(y + c);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float v = to_float<T>(raw[k]);
+          rows_s[(size_t)b * C + c + k] = v;
+          sq[b] += v * v;
+        }
+      }
     }
-    rstd[b] = rsqrtf(block_sum(sq, scratch) / (float)C + eps);
   }
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float total = 0.f;
-    for (int b = 0; b < a.n; ++b)
-      total += to_float<T>(reinterpret_cast<const T*>(a.y[b])[row * C + c]) * rstd[b] * a.gain[(size_t)b * C + c];
-    out[row * C + c] = from_float<T>(total * scale);
+#pragma unroll
+  for (int b = 0; b < 4; ++b)
+    if (b < a.n) rstd[b] = rsqrtf(block_sum(sq[b], scratch) / (float)C + eps);
+  for (int c = V * threadIdx.x; c < C; c += V * blockDim.x) {  // every thread reads back what it wrote
+    __align__(16) T res[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float total = 0.f;
+      for (int b = 0; b < a.n; ++b) total += rows_s[(size_t)b * C + c + k] * rstd[b] * a.gain[(size_t)b * C + c + k];
+      res[k] = from_float<T>(total * scale);
+    }
+    if (V == 1) out[row * C + c] = res[0];
+    else *reinterpret_cast<uint4*>(out + row * C + c) = *reinterpret_cast<const uint4*>(res);
   }
 }
 
-// act 0: silu, 1: tanh-GELU, 4: xIELU with pa = softplus(p), pb = 1/2 + softplus(q)
-template <typename T>
-__global__ void act_rows_kernel(T* __restrict__ out, const T* __restrict__ z, int z_stride, int rows, int I, int act,
-                                float pa, float pb) {
+__device__ __forceinline__ float act_value(float v, int act, float pa, float pb) {
+  if (act == 4) return v > 0.f ? pa * v * v + 0.5f * v : pb * (expm1f(v) - v) + 0.5f * v;
+  if (act == 1) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  return v / (1.0f + expf(-v));
+}
+
+// act 0: silu, 1: tanh-GELU, 4: xIELU with pa = softplus(p), pb = 1/2 + softplus(q). One block row (blockIdx.y) and
+// column chunk; V elements (16 bytes) a thread at a time where the row allows it.
+template <typename T, int V>
+__global__ void act_rows_kernel(T* __restrict__ out, const T* __restrict__ z, int z_stride, int I, int act, float pa,
+                                float pb) {
   grid_launch_dependents();
   grid_dependency_wait();
-  const long long total = (long long)rows * I;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / I;
-    const int c = (int)(i % I);
-    const float v = to_float<T>(z[r * z_stride + c]);
-    float y;
-    if (act == 4) y = v > 0.f ? pa * v * v + 0.5f * v : pb * (expm1f(v) - v) + 0.5f * v;
-    else if (act == 1) y = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-    else y = v / (1.0f + expf(-v));
-    out[i] = from_float<T>(y);
+  const size_t r = blockIdx.y;
+  const T* src = z + r * z_stride;
+  T* dst = out + r * I;
+  for (int c = V * (blockIdx.x * blockDim.x + threadIdx.x); c < I; c += V * gridDim.x * blockDim.x) {
+    __align__(16) T raw[V];
+    __align__(16) T res[V];
+    if (V == 1) raw[0] = src[c];
+    else *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) res[k] = from_float<T>(act_value(to_float<T>(raw[k]), act, pa, pb));
+    if (V == 1) dst[c] = res[0];
+    else *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(res);
   }
 }
 
@@ -502,21 +531,44 @@ KRK_API int krk_norm_sum(void* out, const void* y0, const void* y1, const void* 
   a.y[0] = y0; a.y[1] = y1; a.y[2] = y2; a.y[3] = y3;
   a.gain = gain;
   a.n = n;
-  const int threads = C >= 2048 ? 512 : (C >= 512 ? 256 : 128);
-  if (dtype == KRK_DTYPE_F32)
-    return (int)launch_pdl(norm_sum_kernel<float>, dim3(rows), dim3(threads), 0, stream, (float*)out, a, C, eps, scale);
-  return (int)launch_pdl(norm_sum_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (bf16*)out, a, C, eps, scale);
+  const size_t smem = (size_t)n * C * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  const int V = dtype == KRK_DTYPE_F32 ? 4 : 8;
+  const bool vec = C % V == 0 && (((uintptr_t)out | (uintptr_t)y0 | (uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)y3) & 15) == 0;
+  const int pieces = vec ? C / V : C;
+  const int threads = pieces >= 512 ? 256 : 128;
+  if (dtype == KRK_DTYPE_F32) {
+    auto kern = vec ? norm_sum_kernel<float, 4> : norm_sum_kernel<float, 1>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (float*)out, a, C, eps, scale);
+  }
+  auto kern = vec ? norm_sum_kernel<bf16, 8> : norm_sum_kernel<bf16, 1>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (bf16*)out, a, C, eps, scale);
 }
 
 KRK_API int krk_act_rows(void* out, const void* z, int z_stride, int rows, int I, int act, float pa, float pb, int dtype,
                          cudaStream_t stream) {
   if (rows == 0 || I == 0) return 0;
-  if (act != 0 && act != 1 && act != 4) return -2;
-  const long long total = (long long)rows * I;
-  const int blocks = (int)min((total + 255) / 256, (long long)148 * 16);
-  if (dtype == KRK_DTYPE_F32)
-    return (int)launch_pdl(act_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, (const float*)z, z_stride,
-                           rows, I, act, pa, pb);
-  return (int)launch_pdl(act_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)out, (const bf16*)z, z_stride, rows,
-                         I, act, pa, pb);
+  if ((act != 0 && act != 1 && act != 4) || rows > 65535 * 16) return -2;
+  const int V = dtype == KRK_DTYPE_F32 ? 4 : 8;
+  const bool vec = I % V == 0 && z_stride % V == 0 && (((uintptr_t)out | (uintptr_t)z) & 15) == 0;
+  const int pieces = vec ? I / V : I;
+  const int chunks = min(64, (pieces + 255) / 256);
+  // rows beyond a grid's second dimension are taken in slices
+  const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
+  for (int r0 = 0; r0 < rows; r0 += 65535) {
+    const int nr = min(65535, rows - r0);
+    void* o = (char*)out + (size_t)r0 * I * esz;
+    const void* src = (const char*)z + (size_t)r0 * z_stride * esz;
+    cudaError_t e;
+    if (dtype == KRK_DTYPE_F32)
+      e = launch_pdl(vec ? act_rows_kernel<float, 4> : act_rows_kernel<float, 1>, dim3(chunks, nr), dim3(256), 0, stream,
+                     (float*)o, (const float*)src, z_stride, I, act, pa, pb);
+    else
+      e = launch_pdl(vec ? act_rows_kernel<bf16, 8> : act_rows_kernel<bf16, 1>, dim3(chunks, nr), dim3(256), 0, stream,
+                     (bf16*)o, (const bf16*)src, z_stride, I, act, pa, pb);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
 }

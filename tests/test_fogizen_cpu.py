@@ -157,3 +157,14 @@ def test_random_weights_by_preset_name_build_a_model():
         cfg = preset_config(name)
         tree = PartTree(get_architecture("Fogizen").plan(cfg))
         assert "l0.mix.left.talk" in tree.expected_tensors()
+
+
+def test_command_line_writes_a_preset_as_a_model_folder(tmp_path, capsys):
+    from kernel_rush_kawk_b200 import cli, read_config
+
+    assert cli.main(["write-random", "--preset", "fogizen_tiny", "--seed", "1", "--out", str(tmp_path / "m")]) == 0
+    arch, cfg = read_config(tmp_path / "m")
+    assert arch.name == "Fogizen" and len(cfg.layers) == 3
+    eng = cpu_engine(tmp_path / "m", max_tokens=256, max_context=256)
+    steps = list(eng.generate([[5, 6, 7], [9]], 3))
+    assert len(steps) == 3 and all(len(s) == 2 for s in steps)

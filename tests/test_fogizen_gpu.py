@@ -493,3 +493,23 @@ def test_trace_replay_serves_the_design(folders, tmp_path):
     for t in range(10):
         row = torch.from_numpy(np.fromfile(tmp_path / "o" / f"{1 + t}.f32", dtype="<f4").reshape(1, -1))
         assert_logits(row, ref_a[60 + t:61 + t], "float32", f"replayed token {t}")
+
+
+def test_command_line_writes_a_random_model_and_generates_from_it(tmp_path, capsys):
+    """`write-random` (a preset's configuration and seeded weights as a model folder), then `generate` from that folder
+    and straight from the preset's name: the same weights, so the same greedy tokens; with a temperature the
+    sampler's own seed decides."""
+    from kernel_rush_kawk_b200 import cli
+
+    assert cli.main(["write-random", "--preset", "fogizen_tiny", "--seed", "3", "--out", str(tmp_path / "m")]) == 0
+    capsys.readouterr()
+    common = ["--prompt-ids", "5,6,7,8,9", "--prompt-ids", "11", "--max-new-tokens", "6", "--max-context", "256"]
+    assert cli.main(["generate", "--model", str(tmp_path / "m")] + common) == 0
+    from_folder = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert cli.main(["generate", "--random", "fogizen_tiny", "--weights-seed", "3"] + common) == 0
+    from_preset = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert from_folder == from_preset and [len(r["tokens"]) for r in from_folder] == [6, 6]
+    assert cli.main(["generate", "--random", "fogizen_tiny", "--weights-seed", "3", "--temperature", "0.8", "--seed", "4"]
+                    + common) == 0
+    sampled = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert all(0 <= t < 512 for r in sampled for t in r["tokens"])
