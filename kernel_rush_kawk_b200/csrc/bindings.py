@@ -86,7 +86,6 @@ _MOE_SIGNATURES = {
     "krk_moe_combine": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
 }
 _SCAN_SIGNATURES = {
-    "krk_shift_project": [_P, c_int, _P, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, _P],
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
@@ -925,38 +924,6 @@ class Kernels:
                                           C, rows, batch.row_seq.data_ptr(), batch.cu_q.data_ptr(),
                                           batch.seq_slot.data_ptr(), _code(h.dtype), self._stream(), int(store)), "token shift")
         return out
-
-    SHIFT_PROJECT_MAX_ROWS = 16  # rows up to which the blends and their products run as one launch
-
-    def shift_project(self, h, last_state, mu, weights, batch):
-        """The products W_s (h + (h_prev - h) * mu[s]) of time mixing, one 2-D view [rows, n_s] per blend s. Few rows: one
-        launch that builds each blend in shared memory and multiplies (the views are column ranges of one buffer); many
-        rows: the blends in a kernel of their own, then a product each."""
-        rows, C = h.shape
-        if rows > self.SHIFT_PROJECT_MAX_ROWS or len(weights) > 8 or rows * C * 4 > 200 * 1024:
-            mixes = self.token_shift(h, last_state, mu, batch)
-            return [self.linear(mixes[i], w) for i, w in enumerate(weights)]
-        ptr, stride = self._rows_view(h)
-        if any(w.dtype != h.dtype or w.shape[1] != C or not w.is_contiguous() for w in weights) or mu.shape != (len(weights), C):
-            raise KernelError("the blends' weights are contiguous [n, C] matrices of the path's dtype, one per row of mu")
-        key = ("shift_project", tuple(w.data_ptr() for w in weights))
-        plan = self._partials.get(key)
-        if plan is None:
-            sizes = [w.shape[0] for w in weights]
-            cols, total = [], 0
-            for n in sizes:
-                cols.append(total)
-                total += -(-n // 8) * 8  # every blend's columns start on 16 bytes
-            n = len(weights)
-            plan = self._partials[key] = ((_P * n)(*[w.data_ptr() for w in weights]), (c_int * n)(*sizes), (c_int * n)(*cols),
-                                          sizes, cols, total)
-        wptr, nptr, cptr, sizes, cols, total = plan
-        out = torch.empty((rows, total), dtype=h.dtype, device=h.device)
-        self._ok(self.scan.krk_shift_project(out.data_ptr(), total, ptr, stride, last_state.data_ptr(), mu.data_ptr(),
-                                            len(weights), wptr, nptr, cptr, C, rows, batch.row_seq.data_ptr(),
-                                            batch.cu_q.data_ptr(), batch.seq_slot.data_ptr(), _code(h.dtype),
-                                            self._stream()), "time mixing's blends and products")
-        return [out[:, c:c + n] for c, n in zip(cols, sizes)]
 
     def linear_recurrence(self, kind, r, k, v, gate, lora, w2, w0, heads, dim, norm_w, eps, state, batch, out, out_col,
                           out_scale, rate=None, rate_bias=None, decay_scale=1.0, bonus=None, last_rows=None):

@@ -47,45 +47,6 @@ __global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h,
   }
 }
 
-// Few rows: the blends of time mixing and the products that read them in one launch. Block (feature tile, blend s)
-// builds x_s[r] = h[r] + (prev[r] - h[r]) * mu[s] for every row in shared memory (rounded to T, as the kernel of its own
-// leaves them) and a warp then takes an output feature f of blend s: y[r, col_s + f] = W_s[f] . x_s[r], float32 sums.
-struct ShiftProjectArgs {
-  const void* w[8];  // W_s [n_s, C], element type of the path
-  int n[8];          // output features of blend s
-  int col[8];        // first output column of blend s
-};
-constexpr int SP_WARPS = 8;
-
-template <typename T>
-__global__ void __launch_bounds__(SP_WARPS * 32)
-shift_project_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ h, int h_stride,
-                     const float* __restrict__ last_state, const float* __restrict__ mu, ShiftProjectArgs a, int C, int rows,
-                     const int* __restrict__ row_seq, const int* __restrict__ cu_q, const int* __restrict__ seq_slot) {
-  extern __shared__ __align__(16) float xs[];  // [rows][C]
-  const int s = blockIdx.y;
-  if (blockIdx.x * SP_WARPS >= a.n[s]) return;
-  grid_launch_dependents();
-  grid_dependency_wait();
-  const float* m = mu + (size_t)s * C;
-  for (int i = threadIdx.x; i < rows * C; i += blockDim.x) {
-    const int r = i / C, c = i % C;
-    const int seq = row_seq[r];
-    const float hv = to_float<T>(h[(size_t)r * h_stride + c]);
-    const float pv = cu_q[seq] == r ? last_state[(size_t)seq_slot[seq] * C + c] : to_float<T>(h[(size_t)(r - 1) * h_stride + c]);
-    xs[i] = round_to<T>(hv + (pv - hv) * m[c]);
-  }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int f = blockIdx.x * SP_WARPS + warp;
-  if (f >= a.n[s]) return;
-  const T* w = reinterpret_cast<const T*>(a.w[s]) + (size_t)f * C;
-  for (int r = 0; r < rows; ++r) {
-    const float y = warp_sum(lane_dot<T>(w, xs + (size_t)r * C, C, lane));
-    if (lane == 0) out[(size_t)r * out_stride + a.col[s] + f] = from_float<T>(y);
-  }
-}
-
 struct ScanArgs {
   const void *r, *k, *v, *g, *rate, *lora;
   int r_stride, k_stride, v_stride, g_stride, rate_stride, lora_stride;
@@ -659,33 +620,6 @@ KRK_API int krk_token_shift(void* out, const void* h, int h_stride, float* last_
                            h_stride, last_state, mu, n_mix, C, rows, row_seq, cu_q, seq_slot, store);
   return (int)launch_pdl(token_shift_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (bf16*)out, (const bf16*)h,
                          h_stride, last_state, mu, n_mix, C, rows, row_seq, cu_q, seq_slot, store);
-}
-
-// w: n_mix pointers to W_s [n_s, C]; out [rows, out_stride] receives blend s's product in columns col_s .. col_s + n_s - 1.
-KRK_API int krk_shift_project(void* out, int out_stride, const void* h, int h_stride, const float* last_state, const float* mu,
-                              int n_mix, const void* const* w, const int* n, const int* col, int C, int rows,
-                              const int* row_seq, const int* cu_q, const int* seq_slot, int dtype, cudaStream_t stream) {
-  if (rows == 0) return 0;
-  if (n_mix < 1 || n_mix > 8) return -2;
-  const size_t smem = (size_t)rows * C * sizeof(float);
-  if (smem > 200 * 1024) return -2;
-  ShiftProjectArgs a;
-  int most = 0;
-  for (int s = 0; s < n_mix; ++s) {
-    a.w[s] = w[s];
-    a.n[s] = n[s];
-    a.col[s] = col[s];
-    most = max(most, n[s]);
-  }
-  dim3 grid((most + SP_WARPS - 1) / SP_WARPS, n_mix);
-  if (dtype == KRK_DTYPE_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(shift_project_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return (int)launch_pdl(shift_project_kernel<float>, grid, dim3(SP_WARPS * 32), smem, stream, (float*)out, out_stride,
-                           (const float*)h, h_stride, last_state, mu, a, C, rows, row_seq, cu_q, seq_slot);
-  }
-  if (smem > 48 * 1024) cudaFuncSetAttribute(shift_project_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return (int)launch_pdl(shift_project_kernel<bf16>, grid, dim3(SP_WARPS * 32), smem, stream, (bf16*)out, out_stride,
-                         (const bf16*)h, h_stride, last_state, mu, a, C, rows, row_seq, cu_q, seq_slot);
 }
 
 KRK_API int krk_linear_recurrence(int rule, const void* r, int r_stride, const void* k, int k_stride, const void* v,

@@ -115,9 +115,9 @@ class TimeMixWKV(Branch):
         ops = ctx.ops
         state, last = cache
         rows = h.tensor() if not isinstance(h, torch.Tensor) else h
+        mixes = ops.token_shift(rows, last.state, self.mu, ctx.batch)  # [5, rows, hidden]
         HN = self.channels
-        # each projection of its own blend of the row and the one before it; few rows: blends and products in one launch
-        r, k, v, g, lora = ops.shift_project(rows, last.state, self.mu, self.w_proj, ctx.batch)
+        r, k, v, g, lora = (ops.linear(mixes[i], w) for i, w in enumerate(self.w_proj))
         out = torch.empty((rows.shape[0], HN), dtype=r.dtype, device=r.device)
         ops.linear_recurrence("wkv", r[:, :HN], k[:, :HN], v[:, :HN], g[:, :HN], lora[:, :self.rank], self.w2, self.w0,
                               self.heads, self.dim, self.norm_w, self.eps, state.state, ctx.batch, out, 0, 1.0,

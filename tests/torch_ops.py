@@ -529,10 +529,6 @@ class _WideOps:
             row0 += n
         return (hf[None] + (prev - hf)[None] * mu.float()[:, None, :]).to(h.dtype)
 
-    def shift_project(self, h, last_state, mu, weights, batch):
-        mixes = self.token_shift(h, last_state, mu, batch)
-        return [self.linear(mixes[i], w) for i, w in enumerate(weights)]
-
     def linear_recurrence(self, kind, r, k, v, gate, lora, w2, w0, heads, dim, norm_w, eps, state, batch, out, out_col,
                           out_scale, rate=None, rate_bias=None, decay_scale=1.0, bonus=None, last_rows=None):
         rows, H, N = r.shape[0], heads, dim
