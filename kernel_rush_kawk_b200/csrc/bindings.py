@@ -841,7 +841,7 @@ class Kernels:
             proj.shape[0], int(getattr(cache, "keep_pages", 0)), _code(proj.dtype), self._stream()),
             "biases + head norms + rotation + cache write")
 
-    MIXED_SPLITS_MAX = 8  # blocks that share one sequence's keys in a single-token step
+    MIXED_SPLITS_MAX = 32  # blocks that share one sequence's keys in a single-token step
 
     def mixed_attention(self, proj, q_col, heads, dim, vdim, sink, talk, scale, chunk, batch, cache, out, out_col, out_scale,
                         gate=None):

@@ -151,13 +151,21 @@ template <typename T> __device__ __forceinline__ float dot_key(const float* q, c
 template <> __device__ __forceinline__ float dot_key<bf16>(const float* q, const bf16* k, int D) {
   float dot = 0.f;
   if ((D & 7) == 0) {
-    for (int d = 0; d < D; d += 8) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int d = 0; d < D; d += 32) {  // four 16-byte pieces are requested before the first is used
+      uint4 raw[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        dot += q[d + 2 * j] * __low2float(p[j]);
-        dot += q[d + 2 * j + 1] * __high2float(p[j]);
+      for (int u = 0; u < 4; ++u)
+        if (d + 8 * u < D) raw[u] = *reinterpret_cast<const uint4*>(k + d + 8 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (d + 8 * u < D) {
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            dot += q[d + 8 * u + 2 * j] * __low2float(p[j]);
+            dot += q[d + 8 * u + 2 * j + 1] * __high2float(p[j]);
+          }
+        }
       }
     }
   } else {
@@ -166,11 +174,25 @@ template <> __device__ __forceinline__ float dot_key<bf16>(const float* q, const
   return dot;
 }
 
+// four consecutive elements of a value row (or zeros)
+template <typename T> __device__ __forceinline__ void load4v(const T* p, float* f, bool on);
+template <> __device__ __forceinline__ void load4v<float>(const float* p, float* f, bool on) {
+  const float4 v = on ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4v<bf16>(const bf16* p, float* f, bool on) {
+  const uint2 raw = on ? *reinterpret_cast<const uint2*>(p) : make_uint2(0u, 0u);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  f[0] = __low2float(h[0]); f[1] = __high2float(h[0]); f[2] = __low2float(h[1]); f[3] = __high2float(h[1]);
+}
+
 constexpr int MIX_VPL = 8;  // value heads up to 256
 
 // The walk of one warp (= one query head of one row) over the 32-key chunks base = lo + 32 * (c0 + n * cstep), up to hi,
-// together with the block's other warps. Leaves the running (m, l, acc).
-template <typename T>
+// together with the block's other warps. Leaves the running (m, l, acc). A lane's accumulators are elements lane + 32 i
+// of the value head, or (V4: value heads of a multiple of 4 up to 128 elements) elements 4 lane .. 4 lane + 3, read
+// as one piece per key, eight keys' pieces requested before the first is used.
+template <typename T, bool V4>
 __device__ __forceinline__ void mixed_walk(const float* qs, float* s_buf, const float* talk_s, int HQ, int HKV, int head,
                                            int D, int DV, int slot, int lo, int hi, int c0, int cstep,
                                            const int* __restrict__ table, int width, const T* __restrict__ k_cache,
@@ -204,22 +226,42 @@ __device__ __forceinline__ void mixed_walk(const float* qs, float* s_buf, const 
 #pragma unroll
     for (int i = 0; i < MIX_VPL; ++i) acc[i] *= alpha;
     const int n = min(32, hi - base + 1);
-#pragma unroll 4
-    for (int j = 0; j < n; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const int page = __shfl_sync(0xffffffffu, my_page, j);  // lane j looked its key's page up already
-      const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + ((base + j) % KRK_PAGE)) * DV;
+    if (V4) {
+      const bool mine = 4 * lane < DV;
+      for (int j0 = 0; j0 < n; j0 += 8) {
+        float v[8][4];
 #pragma unroll
-      for (int i = 0; i < MIX_VPL; ++i) {
-        const int d = lane + 32 * i;
-        if (d < DV) acc[i] += pj * to_float<T>(vp[d]);
+        for (int u = 0; u < 8; ++u) {
+          const int j = j0 + u;
+          const int page = __shfl_sync(0xffffffffu, my_page, j & 31);  // lane j looked its key's page up already
+          const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + ((base + j) % KRK_PAGE)) * DV + 4 * lane;
+          load4v<T>(vp, v[u], mine && j < n);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float pj = __shfl_sync(0xffffffffu, p, (j0 + u) & 31);  // 0 for a lane beyond the last key
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i] += pj * v[u][i];
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int j = 0; j < n; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const int page = __shfl_sync(0xffffffffu, my_page, j);  // lane j looked its key's page up already
+        const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + ((base + j) % KRK_PAGE)) * DV;
+#pragma unroll
+        for (int i = 0; i < MIX_VPL; ++i) {
+          const int d = lane + 32 * i;
+          if (d < DV) acc[i] += pj * to_float<T>(vp[d]);
+        }
       }
     }
     m = m_new;
   }
 }
 
-template <typename T>
+template <typename T, bool V4>
 __global__ void mixed_attention_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
                                        const T* __restrict__ proj, int stride, int q_col, int HQ, int HKV, int D, int DV,
                                        const float* __restrict__ sink, const float* __restrict__ talk,
@@ -248,21 +290,21 @@ __global__ void mixed_attention_kernel(T* __restrict__ out, int out_stride, int 
   float acc[MIX_VPL];
 #pragma unroll
   for (int i = 0; i < MIX_VPL; ++i) acc[i] = 0.f;
-  mixed_walk<T>(q_s + (size_t)head * D, s_buf, talk ? talk_s : nullptr, HQ, HKV, head, D, DV, slot, lo, pos, 0, 1, table,
+  mixed_walk<T, V4>(q_s + (size_t)head * D, s_buf, talk ? talk_s : nullptr, HQ, HKV, head, D, DV, slot, lo, pos, 0, 1, table,
                 width, k_cache, v_cache, scale, m, l, acc);
   T* o = out + (size_t)row * out_stride + out_col + (size_t)head * DV;
   float inv = out_scale / l;
   if (gate_mode == 1) inv *= sigmoid_(to_float<T>(gate[(size_t)row * gate_stride + gate_col + head]));
 #pragma unroll
   for (int i = 0; i < MIX_VPL; ++i) {
-    const int d = lane + 32 * i;
-    if (d < DV) o[d] = from_float<T>(acc[i] * inv);
+    const int d = V4 ? 4 * lane + i : lane + 32 * i;
+    if ((!V4 || i < 4) && d < DV) o[d] = from_float<T>(acc[i] * inv);
   }
 }
 
 // One token per sequence: block (split, sequence) takes every SPL-th 32-key chunk and leaves its share in
 // scratch [seq][head][SPL][DV + 2] as (m, l, acc[DV]).
-template <typename T>
+template <typename T, bool V4>
 __global__ void mixed_attention_single_kernel(float* __restrict__ scratch, const T* __restrict__ proj, int stride, int q_col,
                                               int HQ, int HKV, int D, int DV, const float* __restrict__ sink,
                                               const float* __restrict__ talk, const int* __restrict__ seq_slot,
@@ -291,7 +333,7 @@ __global__ void mixed_attention_single_kernel(float* __restrict__ scratch, const
   float acc[MIX_VPL];
 #pragma unroll
   for (int i = 0; i < MIX_VPL; ++i) acc[i] = 0.f;
-  mixed_walk<T>(q_s + (size_t)head * D, s_buf, talk ? talk_s : nullptr, HQ, HKV, head, D, DV, slot, lo, pos, split, SPL,
+  mixed_walk<T, V4>(q_s + (size_t)head * D, s_buf, talk ? talk_s : nullptr, HQ, HKV, head, D, DV, slot, lo, pos, split, SPL,
                 table, width, k_cache, v_cache, scale, m, l, acc);
   float* dst = scratch + (((size_t)seq * HQ + head) * SPL + split) * (DV + 2);
   if (lane == 0) {
@@ -300,8 +342,8 @@ __global__ void mixed_attention_single_kernel(float* __restrict__ scratch, const
   }
 #pragma unroll
   for (int i = 0; i < MIX_VPL; ++i) {
-    const int d = lane + 32 * i;
-    if (d < DV) dst[2 + d] = acc[i];
+    const int d = V4 ? 4 * lane + i : lane + 32 * i;
+    if ((!V4 || i < 4) && d < DV) dst[2 + d] = acc[i];
   }
 }
 
@@ -470,20 +512,17 @@ KRK_API int krk_mixed_attention(void* out, int out_stride, int out_col, float ou
   if (HQ < 1 || HQ > 32 || HKV < 1 || HQ % HKV || DV > 32 * MIX_VPL || gate_mode > 1 || chunk < 0) return -2;
   const size_t smem = mixed_smem(HQ, D, talk != nullptr);
   if (smem > 200 * 1024) return -2;
-  if (dtype == KRK_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(mixed_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return (int)launch_pdl(mixed_attention_kernel<float>, dim3(rows), dim3(HQ * 32), smem, stream, (float*)out, out_stride,
-                           out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, row_seq, row_pos,
-                           seq_slot, table, width, (const float*)k_cache, (const float*)v_cache, scale, chunk,
-                           (const float*)gate, gate_stride, gate_col, gate_mode);
-  }
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(mixed_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return (int)launch_pdl(mixed_attention_kernel<bf16>, dim3(rows), dim3(HQ * 32), smem, stream, (bf16*)out, out_stride,
-                         out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, row_seq, row_pos,
-                         seq_slot, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, chunk, (const bf16*)gate,
-                         gate_stride, gate_col, gate_mode);
+  const bool v4 = DV % 4 == 0 && DV <= 128;
+  auto go = [&](auto kern, auto* tag) {
+    typedef decltype(tag) P;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(kern, dim3(rows), dim3(HQ * 32), smem, stream, (P)out, out_stride, out_col, out_scale, (P)proj,
+                           stride, q_col, HQ, HKV, D, DV, sink, talk, row_seq, row_pos, seq_slot, table, width, (P)k_cache,
+                           (P)v_cache, scale, chunk, (P)gate, gate_stride, gate_col, gate_mode);
+  };
+  if (dtype == KRK_DTYPE_F32)
+    return v4 ? go(mixed_attention_kernel<float, true>, (float*)nullptr) : go(mixed_attention_kernel<float, false>, (float*)nullptr);
+  return v4 ? go(mixed_attention_kernel<bf16, true>, (bf16*)nullptr) : go(mixed_attention_kernel<bf16, false>, (bf16*)nullptr);
 }
 
 // scratch: n_seqs * HQ * splits * (DV + 2) floats
@@ -500,27 +539,22 @@ KRK_API int krk_mixed_attention_single(void* out, int out_stride, int out_col, f
   const size_t smem = mixed_smem(HQ, D, talk != nullptr);
   if (smem > 200 * 1024) return -2;
   const int merge_blocks = (n_seqs * HQ + 3) / 4;
-  cudaError_t e;
-  if (dtype == KRK_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(mixed_attention_single_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_pdl(mixed_attention_single_kernel<float>, dim3(splits, n_seqs), dim3(HQ * 32), smem, stream, scratch,
-                   (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, seq_slot, seq_start, table, width,
-                   (const float*)k_cache, (const float*)v_cache, scale, chunk, splits);
+  const bool v4 = DV % 4 == 0 && DV <= 128;
+  auto go = [&](auto kern, auto merge, auto* tag) {
+    typedef decltype(tag) P;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = launch_pdl(kern, dim3(splits, n_seqs), dim3(HQ * 32), smem, stream, scratch, (P)proj, stride, q_col, HQ, HKV,
+                               D, DV, sink, talk, seq_slot, seq_start, table, width, (P)k_cache, (P)v_cache, scale, chunk,
+                               splits);
     if (e != cudaSuccess) return (int)e;
-    return (int)launch_pdl(mixed_attention_merge_kernel<float>, dim3(merge_blocks), dim3(128), 0, stream, (float*)out,
-                           out_stride, out_col, out_scale, (const float*)scratch, HQ, DV, splits, n_seqs, (const float*)gate,
-                           gate_stride, gate_col, gate_mode);
-  }
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(mixed_attention_single_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  e = launch_pdl(mixed_attention_single_kernel<bf16>, dim3(splits, n_seqs), dim3(HQ * 32), smem, stream, scratch,
-                 (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, talk, seq_slot, seq_start, table, width,
-                 (const bf16*)k_cache, (const bf16*)v_cache, scale, chunk, splits);
-  if (e != cudaSuccess) return (int)e;
-  return (int)launch_pdl(mixed_attention_merge_kernel<bf16>, dim3(merge_blocks), dim3(128), 0, stream, (bf16*)out, out_stride,
-                         out_col, out_scale, (const float*)scratch, HQ, DV, splits, n_seqs, (const bf16*)gate, gate_stride,
-                         gate_col, gate_mode);
+    return (int)launch_pdl(merge, dim3(merge_blocks), dim3(128), 0, stream, (decltype(tag))out, out_stride, out_col, out_scale,
+                           (const float*)scratch, HQ, DV, splits, n_seqs, (P)gate, gate_stride, gate_col, gate_mode);
+  };
+  if (dtype == KRK_DTYPE_F32)
+    return v4 ? go(mixed_attention_single_kernel<float, true>, mixed_attention_merge_kernel<float>, (float*)nullptr)
+              : go(mixed_attention_single_kernel<float, false>, mixed_attention_merge_kernel<float>, (float*)nullptr);
+  return v4 ? go(mixed_attention_single_kernel<bf16, true>, mixed_attention_merge_kernel<bf16>, (bf16*)nullptr)
+            : go(mixed_attention_single_kernel<bf16, false>, mixed_attention_merge_kernel<bf16>, (bf16*)nullptr);
 }
 
 KRK_API int krk_norm_sum(void* out, const void* y0, const void* y1, const void* y2, const void* y3, int n, const float* gain,
