@@ -409,12 +409,17 @@ __global__ void norm_sum_kernel(T* __restrict__ out, NormSumArgs a, int C, float
         const T* y = reinterpret_cast<const T*>(a.y[b]) + row * C;
         if (V == 1) raw[0] = y[c];
         else *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(y + c);
+        __align__(16) float f[V];
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-          const float v = to_float<T>(raw[k]);
-          rows_s[(size_t)b * C + c + k] = v;
-          sq[b] += v * v;
+          f[k] = to_float<T>(raw[k]);
+          sq[b] += f[k] * f[k];
         }
+        float* dst = rows_s + (size_t)b * C + c;
+        if (V == 1) dst[0] = f[0];
+        else
+#pragma unroll
+          for (int k = 0; k < V; k += 4) *reinterpret_cast<float4*>(dst + k) = *reinterpret_cast<const float4*>(f + k);
       }
     }
   }
@@ -423,12 +428,26 @@ __global__ void norm_sum_kernel(T* __restrict__ out, NormSumArgs a, int C, float
     if (b < a.n) rstd[b] = rsqrtf(block_sum(sq[b], scratch) / (float)C + eps);
   for (int c = V * threadIdx.x; c < C; c += V * blockDim.x) {  // every thread reads back what it wrote
     __align__(16) T res[V];
+    __align__(16) float total[V];
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      float total = 0.f;
-      for (int b = 0; b < a.n; ++b) total += rows_s[(size_t)b * C + c + k] * rstd[b] * a.gain[(size_t)b * C + c + k];
-      res[k] = from_float<T>(total * scale);
+    for (int k = 0; k < V; ++k) total[k] = 0.f;
+    for (int b = 0; b < a.n; ++b) {
+      __align__(16) float f[V], g[V];
+      if (V == 1) {
+        f[0] = rows_s[(size_t)b * C + c];
+        g[0] = a.gain[(size_t)b * C + c];
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; k += 4) {
+          *reinterpret_cast<float4*>(f + k) = *reinterpret_cast<const float4*>(rows_s + (size_t)b * C + c + k);
+          *reinterpret_cast<float4*>(g + k) = *reinterpret_cast<const float4*>(a.gain + (size_t)b * C + c + k);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < V; ++k) total[k] += f[k] * rstd[b] * g[k];
     }
+#pragma unroll
+    for (int k = 0; k < V; ++k) res[k] = from_float<T>(total[k] * scale);
     if (V == 1) out[row * C + c] = res[0];
     else *reinterpret_cast<uint4*>(out + row * C + c) = *reinterpret_cast<const uint4*>(res);
   }
