@@ -359,15 +359,19 @@ __global__ void mixed_attention_merge_kernel(T* __restrict__ out, int out_stride
   if (item >= n_seqs * HQ) return;
   const int seq = item / HQ, head = item % HQ;
   const float* src = scratch + (size_t)item * SPL * (DV + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < SPL; ++s) m = fmaxf(m, src[(size_t)s * (DV + 2)]);
-  float l = 0.f, acc[MIX_VPL];
+  // lane s holds split s's maximum and sum (up to 32 splits); the outputs are added in split order
+  const float my_m = lane < SPL ? src[(size_t)lane * (DV + 2)] : -INFINITY;
+  const float my_l = lane < SPL ? src[(size_t)lane * (DV + 2) + 1] : 0.f;
+  const float m = warp_max(my_m);
+  const float my_w = lane < SPL ? expf(my_m - m) : 0.f;  // a split without keys left (-inf, 0, 0): weight 0
+  const float l = warp_sum(my_w * my_l);
+  float acc[MIX_VPL];
 #pragma unroll
   for (int i = 0; i < MIX_VPL; ++i) acc[i] = 0.f;
+#pragma unroll 8
   for (int s = 0; s < SPL; ++s) {
     const float* p = src + (size_t)s * (DV + 2);
-    const float w = expf(p[0] - m);  // a split without keys left (-inf, 0, 0): weight 0
-    l += w * p[1];
+    const float w = __shfl_sync(0xffffffffu, my_w, s);
 #pragma unroll
     for (int i = 0; i < MIX_VPL; ++i) {
       const int d = lane + 32 * i;
@@ -423,9 +427,21 @@ __global__ void norm_sum_kernel(T* __restrict__ out, NormSumArgs a, int C, float
       }
     }
   }
+  {  // the inputs' sums of squares through one exchange
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
 #pragma unroll
-  for (int b = 0; b < 4; ++b)
-    if (b < a.n) rstd[b] = rsqrtf(block_sum(sq[b], scratch) / (float)C + eps);
+    for (int b = 0; b < 4; ++b) sq[b] = warp_sum(sq[b]);
+    if (lane == 0)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) scratch[b * 8 + warp] = sq[b];
+    __syncthreads();
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      float t = 0.f;
+      for (int w = 0; w < n_warps; ++w) t += scratch[b * 8 + w];
+      rstd[b] = rsqrtf(t / (float)C + eps);
+    }
+  }
   for (int c = V * threadIdx.x; c < C; c += V * blockDim.x) {  // every thread reads back what it wrote
     __align__(16) T res[V];
     __align__(16) float total[V];
@@ -553,7 +569,7 @@ KRK_API int krk_mixed_attention_single(void* out, int out_stride, int out_col, f
                                        int gate_mode, int dtype, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (HQ < 1 || HQ > 32 || HKV < 1 || HQ % HKV || DV > 32 * MIX_VPL || gate_mode > 1 || chunk < 0 || splits < 1 ||
-      n_seqs > 65535)
+      splits > 32 || n_seqs > 65535)
     return -2;
   const size_t smem = mixed_smem(HQ, D, talk != nullptr);
   if (smem > 200 * 1024) return -2;
@@ -589,7 +605,7 @@ KRK_API int krk_norm_sum(void* out, const void* y0, const void* y1, const void* 
   const int V = dtype == KRK_DTYPE_F32 ? 4 : 8;
   const bool vec = C % V == 0 && (((uintptr_t)out | (uintptr_t)y0 | (uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)y3) & 15) == 0;
   const int pieces = vec ? C / V : C;
-  const int threads = pieces >= 512 ? 256 : 128;
+  const int threads = min(256, (pieces + 31) / 32 * 32);  // up to eight warps
   if (dtype == KRK_DTYPE_F32) {
     auto kern = vec ? norm_sum_kernel<float, 4> : norm_sum_kernel<float, 1>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
