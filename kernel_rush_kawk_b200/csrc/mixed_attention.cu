@@ -447,7 +447,9 @@ __global__ void norm_sum_kernel(T* __restrict__ out, NormSumArgs a, int C, float
     __align__(16) float total[V];
 #pragma unroll
     for (int k = 0; k < V; ++k) total[k] = 0.f;
-    for (int b = 0; b < a.n; ++b) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      if (b >= a.n) break;
       __align__(16) float f[V], g[V];
       if (V == 1) {
         f[0] = rows_s[(size_t)b * C + c];
