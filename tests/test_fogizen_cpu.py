@@ -168,3 +168,96 @@ def test_command_line_writes_a_preset_as_a_model_folder(tmp_path, capsys):
     eng = cpu_engine(tmp_path / "m", max_tokens=256, max_context=256)
     steps = list(eng.generate([[5, 6, 7], [9]], 3))
     assert len(steps) == 3 and all(len(s) == 2 for s in steps)
+
+
+# ----------------------------------------------------------------------------------------------
+# the parts alone, with the kernels' plain torch restatement, against the plain functions
+# ----------------------------------------------------------------------------------------------
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g) * scale
+
+
+def _runtime():
+    from kernel_rush_kawk_b200.engine.model import Runtime
+
+    return Runtime(torch.device("cpu"), torch.float32, TorchOps(torch.float32))
+
+
+def _context(rt, slots, starts, token_lists, cache):
+    from kernel_rush_kawk_b200.engine.step import BatchMeta, StepContext
+
+    meta = BatchMeta(sum(len(t) for t in token_lists), len(slots), 0, rt.device)
+    meta.fill(slots, starts, token_lists, [])
+    return StepContext(rt.ops, meta, cache)
+
+
+def _run_mixer(part, rt, h, pieces):
+    from kernel_rush_kawk_b200.cache import SequenceCache
+
+    cache = SequenceCache([part.cache_need()], 512, 1, 512, rt.device, torch.float32)
+    slot = cache.alloc()
+    got, start = [], 0
+    for n in pieces:
+        cache.reserve(slot, start + n)
+        cache.sync()
+        got.append(part.forward(_context(rt, [slot], [start], [[0] * n], cache), h[start:start + n], cache.view(0)))
+        cache.advance(slot, n)
+        start += n
+    return torch.cat(got)
+
+
+def test_the_whole_mixer_of_a_layer_in_pieces_against_the_plain_functions():
+    """The shifted input, the two mixers side by side, their norms and the half sum, as the plan builds them."""
+    import plain_fogizen as plain
+    from kernel_rush_kawk_b200.config.registry import get_architecture
+    from kernel_rush_kawk_b200.parts import mixer_class
+
+    cfg = config("fa")
+    spec = get_architecture("Fogizen").plan(cfg).layers[0].mixer
+    part = mixer_class(spec.kind)(dict(spec.params))
+    w = {key: _rand(tuple(t.shape), 10 + i, 0.3) + (1.0 if t.role == "gain" else 0.0)
+         for i, (key, t) in enumerate(part.tensor_specs().items())}
+    w["inner.left.talk"] = 0.6 * torch.eye(4) + _rand((4, 4), 3, 0.3)
+    rt = _runtime()
+    part.bind(w, rt)
+    T = 45
+    n = _rand((T, 64), 5)
+    ref = {spec.tensors[k]: v.double() for k, v in w.items()}
+    nd = n.double()
+    s = nd + (plain.previous_rows(nd) - nd) * ref["l0.shift"]
+    want = plain.mixer(s, ref, "l0.mix.", CONFIGS["fa"]["layers"][0]["mixer"] | {"right": {"heads": 3, "dim": 16}}, cfg.eps,
+                       torch.arange(T))
+    for pieces in ([T], [9, 1, 2, 33], [20] + [1] * 25):
+        got = _run_mixer(part, rt, n, pieces)
+        assert (got.double() - want).abs().max() < 2e-4 * want.abs().max(), f"pieces {pieces[:4]}"
+
+
+@pytest.mark.parametrize("shape", [(64, 6, 2, 3, 2, 24, 1.5), (96, 4, 4, 4, 4, 16, 0.7), (50, 9, 2, 3, 2, 11, 1.0), (64, 8, 3, 2, 1, 40, 2.5)])
+def test_routing_within_groups_and_the_dense_activation_against_the_plain_functions(shape):
+    import plain_fogizen as plain
+    from types import SimpleNamespace
+    from kernel_rush_kawk_b200.parts import DenseMLP, RoutedExperts
+
+    C, E, top, count, keep, F, scale = shape
+    rt = _runtime()
+    part = RoutedExperts({"hidden": C, "experts": E, "top": top, "intermediate": F, "scoring": "sigmoid_groups",
+                          "groups": count, "keep_groups": keep, "route_scale": scale})
+    w = {"router": _rand((E, C), 1, 0.5), "correction": _rand((E,), 2, 0.6) - 0.5}
+    for e in range(E):
+        w.update({f"e{e}.gate": _rand((F, C), 10 + 3 * e, 0.3), f"e{e}.up": _rand((F, C), 11 + 3 * e, 0.3),
+                  f"e{e}.down": _rand((C, F), 12 + 3 * e, 0.3)})
+    part.bind(w, rt)
+    h = _rand((30, C), 7, 1.5)
+    ref = {k: v.double() for k, v in w.items()}
+    router = {"experts": E, "top": top, "scale": scale, "groups": {"count": count, "keep": keep}}
+    want = plain.routed_ff(h.double(), ref, "", {"router": router})
+    got = part.forward(SimpleNamespace(ops=rt.ops, batch=SimpleNamespace(is_decode=False)), h)
+    assert (got.double() - want).abs().max() < 1e-4 * want.abs().max()
+    dense = DenseMLP({"hidden": C, "intermediate": F, "activation": "xielu"})
+    wd = {"up": _rand((F, C), 3, 0.5), "down": _rand((C, F), 4, 0.3), "act": torch.tensor([0.4, -1.2])}
+    dense.bind(wd, rt)
+    want = plain.dense_ff(h.double(), {k: v.double() for k, v in wd.items()}, "")
+    got = dense.forward(SimpleNamespace(ops=rt.ops), h)
+    assert (got.double() - want).abs().max() < 1e-4 * want.abs().max()
