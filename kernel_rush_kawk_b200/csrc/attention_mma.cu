@@ -468,7 +468,8 @@ mixed_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_scale, co
                      const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                      const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
                      int width, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, float scale,
-                     int chunk, const bf16* __restrict__ gate, int gate_stride, int gate_mode, int ncta, int max_kv) {
+                     int chunk, const bf16* __restrict__ gate, int gate_stride, int gate_mode, int ncta, int max_kv,
+                     float* __restrict__ part) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
@@ -523,8 +524,23 @@ mixed_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_scale, co
   load_q(qf, qp[0], qp[1], lane);
   const int first_pos = start + tile * 16;
   const int last_pos = start + min(q_len - 1, tile * 16 + 15);
-  const int j_lo = (chunk > 0 ? (first_pos / chunk) * chunk : 0) / KRK_PAGE;
-  const int j_hi = last_pos / KRK_PAGE;
+  int j_lo = (chunk > 0 ? (first_pos / chunk) * chunk : 0) / KRK_PAGE;
+  int j_hi = last_pos / KRK_PAGE;
+  // With gridDim.z > 1 the tile's pages are dealt out in runs over that many blocks (or clusters); each leaves
+  // (maximum, sum, output) per row and head in `part`, which a merge kernel adds in order. The sink enters in the first.
+  const int SPL = gridDim.z, split = blockIdx.z;
+  if (SPL > 1) {
+    const int per = (j_hi - j_lo + SPL) / SPL;
+    j_lo += split * per;
+    j_hi = min(j_hi, j_lo + per - 1);
+    if (split > 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.f;
+      }
+    }
+  }
   const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
 
   auto issue = [&](const bf16* cache, int j) {
@@ -647,6 +663,22 @@ mixed_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_scale, co
     __syncthreads();  // before the next K pages overwrite the V pages (and, in one block, the next scores these)
   }
   if (talk && ncta > 1) cluster.sync();  // no block leaves while another may still touch its shared memory
+  if (SPL > 1) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (!op[h]) continue;
+      const int tok = tile * 16 + g + 8 * h;
+      float* dst = part + (((size_t)(row0 + tok) * HQ + head) * SPL + split) * (D + 2);
+      if (t4 == 0) {
+        dst[0] = m[h] / LOG2E;  // the merge works in natural units; -inf stays -inf
+        dst[1] = l[h];
+      }
+#pragma unroll
+      for (int n = 0; n < DTILES; ++n)
+        *reinterpret_cast<float2*>(dst + 2 + n * 8 + 2 * t4) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+    }
+    return;
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!op[h]) continue;
@@ -1637,14 +1669,17 @@ KRK_API int krk_sink_window_prefill(void* out, int out_stride, float out_scale, 
 
 // Attention with mixed head scores over blocks of keys, for steps of many tokens (see mixed_prefill_kernel). q_base,
 // out and gate point at the first query / output / gate column of the wider rows (strides in elements; out and q even).
+// With splits > 1 every tile's pages are dealt out over that many blocks, which leave their shares in `part`
+// (rows * HQ * splits * (D + 2) floats, row = the step's row index) for krk_mixed_attention_merge; `out` is not written.
 // -2: a shape this kernel does not take (the heads do not split evenly over 1, 2, 4 or 8 blocks of at most 16 warps, 12
 // for heads of more than 64 elements, whose pages fit the shared memory).
 KRK_API int krk_mixed_prefill(void* out, int out_stride, float out_scale, const void* q_base, int q_stride, int HQ, int HKV,
                               const float* sink, const float* talk, const int* seq_slot, const int* seq_start,
                               const int* seq_qlen, const int* cu_q, const int* table, int width, const void* k_cache,
                               const void* v_cache, int n_seqs, int max_q_len, float scale, int chunk, const void* gate,
-                              int gate_stride, int gate_mode, cudaStream_t stream) {
+                              int gate_stride, int gate_mode, cudaStream_t stream, int splits, float* part) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
+  if (splits < 1 || splits > 32 || (splits > 1 && !part)) return -2;
   if (HQ < 1 || HQ > MIX_MAX_HEADS || HKV < 1 || HQ % HKV || gate_mode > 1 || chunk < 0 || n_seqs > 65535) return -2;
   if ((out_stride & 1) || (q_stride & 1) || ((uintptr_t)out & 3) || ((uintptr_t)q_base & 3)) return -2;
   const int most = D > 64 ? 12 : 16;  // warps whose accumulators fit a block's registers
@@ -1667,7 +1702,7 @@ KRK_API int krk_mixed_prefill(void* out, int out_stride, float out_scale, const 
   auto launch = [&](auto kern) -> cudaError_t {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(tiles * ncta), n_seqs);
+    cfg.gridDim = dim3((unsigned)(tiles * ncta), n_seqs, splits);
     cfg.blockDim = dim3(hpb * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -1680,7 +1715,7 @@ KRK_API int krk_mixed_prefill(void* out, int out_stride, float out_scale, const 
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, (bf16*)out, out_stride, out_scale, (const bf16*)q_base, q_stride, HQ, HKV, sink, talk,
                               seq_slot, seq_start, seq_qlen, cu_q, table, width, (const bf16*)k_cache, (const bf16*)v_cache,
-                              scale, chunk, (const bf16*)gate, gate_stride, gate_mode, ncta, max_kv);
+                              scale, chunk, (const bf16*)gate, gate_stride, gate_mode, ncta, max_kv, part);
   };
   cudaError_t e;
   if (hpb <= 8) e = launch(mixed_prefill_kernel<8>);

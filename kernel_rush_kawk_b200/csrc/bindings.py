@@ -73,6 +73,7 @@ _MIX_SIGNATURES = {
                             c_int, _P, _P, c_int, c_float, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "krk_mixed_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                                    _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_mixed_attention_merge": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "krk_norm_sum": [_P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_float, c_float, c_int, _P],
     "krk_act_rows": [_P, _P, c_int, c_int, c_int, c_int, c_float, c_float, c_int, _P],
 }
@@ -104,7 +105,7 @@ _ATTN_SIGNATURES = {
     "krk_sink_window_prefill": [_P, c_int, c_float, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
                                 c_int, c_float, c_int, c_int, c_int, _P, c_int, c_int, _P],
     "krk_mixed_prefill": [_P, c_int, c_float, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
-                          c_int, c_float, c_int, _P, c_int, c_int, _P],
+                          c_int, c_float, c_int, _P, c_int, c_int, _P, c_int, _P],
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
@@ -841,6 +842,9 @@ class Kernels:
             proj.shape[0], int(getattr(cache, "keep_pages", 0)), _code(proj.dtype), self._stream()),
             "biases + head norms + rotation + cache write")
 
+    # bytes up to which a prompt step's tiles leave shares to be merged (measured: 51 MB of shares at 12 heads gain
+    # 12 % of the attention's time, 136 MB at 32 heads lose 30 %)
+    MIXED_PREFILL_SCRATCH = 64 << 20
     MIXED_SPLITS_MAX = 32  # blocks that share one sequence's keys in a single-token step
 
     def mixed_attention(self, proj, q_col, heads, dim, vdim, sink, talk, scale, chunk, batch, cache, out, out_col, out_scale,
@@ -877,13 +881,35 @@ class Kernels:
         if (proj.dtype == torch.bfloat16 and dim == vdim and dim in self.attn and hasattr(self.attn[dim], "krk_mixed_prefill")):
             # many tokens per sequence in bfloat16: scores and P.V on the tensor cores (compiled per head size)
             esz = proj.element_size()
+            # Few tiles of unequal length (one prompt of a few thousand tokens: a tile sees 1 to chunk / 64 pages) leave
+            # SMs idle while the longest runs: then every tile's pages are dealt out over 2 or 4 blocks and a merge
+            # kernel adds their shares. By the step's shape; a step of many tokens is never replayed from a graph.
+            rows = proj.shape[0]
+            tiles = -(-batch.max_q_len // 16) * batch.n_seqs
+            pages = -(-min(chunk or batch.max_kv_len, batch.max_kv_len) // 64)
+            splits = 1 if tiles >= 592 or pages < 4 else (2 if tiles >= 296 else 4)
+            splits = min(splits, pages)
+            part = None
+            while splits > 1 and rows * heads * splits * (dim + 2) * 4 > self.MIXED_PREFILL_SCRATCH:
+                splits //= 2  # the shares are written and read once: beyond this size that costs more than it gains
+            if splits > 1:
+                need = rows * heads * splits * (dim + 2)
+                part = self._partials.get("mixed_prefill")
+                if part is None or part.numel() < need:
+                    part = self._partials["mixed_prefill"] = torch.empty(need, dtype=torch.float32, device=self.device)
             rc = self.attn[dim].krk_mixed_prefill(
                 optr + out_col * esz, ostride, float(out_scale), ptr + q_col * esz, stride, heads, cache.kv_heads, _ptr(sink),
                 _ptr(talk), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(),
                 batch.cu_q.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
-                batch.n_seqs, batch.max_q_len, float(scale), chunk, ptr + g_col * esz, stride, g_mode, self._stream())
+                batch.n_seqs, batch.max_q_len, float(scale), chunk, ptr + g_col * esz, stride, g_mode, self._stream(),
+                splits, _ptr(part))
             if rc != -2:  # -2: a shape it does not take; the general kernel does
                 self._ok(rc, "tensor-core attention with mixed scores")
+                if splits > 1:
+                    self._ok(self.mix.krk_mixed_attention_merge(optr, ostride, out_col, float(out_scale), part.data_ptr(), heads,
+                                                               vdim, splits, rows, ptr, stride, g_col, g_mode,
+                                                               _code(proj.dtype), self._stream()),
+                             "merge of a prompt's key splits")
                 return
         self._ok(self.mix.krk_mixed_attention(
             optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),

@@ -594,6 +594,24 @@ KRK_API int krk_mixed_attention_single(void* out, int out_stride, int out_col, f
             : go(mixed_attention_single_kernel<bf16, false>, mixed_attention_merge_kernel<bf16>, (bf16*)nullptr);
 }
 
+// The merge alone, for shares that another kernel left: items = rows of `out` (and of `gate`), scratch
+// [items][HQ][splits][DV + 2] as (maximum, sum, output).
+KRK_API int krk_mixed_attention_merge(void* out, int out_stride, int out_col, float out_scale, const float* scratch, int HQ,
+                                      int DV, int splits, int items, const void* gate, int gate_stride, int gate_col,
+                                      int gate_mode, int dtype, cudaStream_t stream) {
+  if (items == 0) return 0;
+  if (splits < 1 || splits > 32 || DV > 32 * MIX_VPL || gate_mode > 1) return -2;
+  const long long blocks = ((long long)items * HQ + 3) / 4;
+  if (blocks > 0x7fffffffLL) return -3;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(mixed_attention_merge_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, stream, (float*)out,
+                           out_stride, out_col, out_scale, scratch, HQ, DV, splits, items, (const float*)gate, gate_stride,
+                           gate_col, gate_mode);
+  return (int)launch_pdl(mixed_attention_merge_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, stream, (bf16*)out,
+                         out_stride, out_col, out_scale, scratch, HQ, DV, splits, items, (const bf16*)gate, gate_stride,
+                         gate_col, gate_mode);
+}
+
 KRK_API int krk_norm_sum(void* out, const void* y0, const void* y1, const void* y2, const void* y3, int n, const float* gain,
                          int rows, int C, float eps, float scale, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
