@@ -19,10 +19,15 @@
 // row's result depends on that row's keys only, in their order: it is the same to the bit however the tokens were
 // cut into steps or batched. Without `talk` no scores are exchanged.
 //
-// krk_mixed_attention_single (one token per sequence): the keys of a sequence are split over the blocks of a
-// cluster-free grid (sequence, split); every block does what the general kernel does over its share of the 32-key
-// chunks and leaves (maximum, sum, output) per head; krk_mixed_attention_merge adds the shares in split order. The
-// sink enters once, in the first split.
+// krk_mixed_attention_single (one token per sequence): the keys of a sequence are split over up to 32 blocks of a grid
+// (split, sequence); every block does what the general kernel does over its share of the 32-key chunks and leaves
+// (maximum, sum, output) per head; krk_mixed_attention_merge (one warp per (row, head), a lane per share for the
+// maxima and sums) adds the shares in split order. The sink enters once, in the first split. The merge alone also
+// serves the tensor-core prompt kernel where that deals a tile's pages out over several blocks.
+//
+// In both kernels a lane takes four consecutive elements of a value row as one piece per key, eight keys' pieces
+// requested before the first is used, where the value head is a multiple of 4 up to 128 elements (else element
+// lane + 32 i of every row), and a key row arrives four 16-byte pieces at a time.
 //
 // krk_norm_sum: out = scale * sum_b y_b / sqrt(mean(y_b^2) + eps) * gain_b over up to four inputs, float32 inside.
 // krk_act_rows: an activation without a gate, elementwise (xIELU with its two slopes, tanh-GELU, SiLU).
