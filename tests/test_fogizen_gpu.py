@@ -154,6 +154,9 @@ LEFT_SHAPES = [  # hidden, heads, kv heads, dim, vdim, block, rotated, base, fac
     (64, 8, 2, 64, 64, 64, 64, 500.0, 8.0),
     (32, 1, 1, 16, 24, None, 0, 1.0, 1.0),
     (40, 5, 1, 10, 6, 128, 10, 50.0, 2.0),
+    (64, 13, 13, 16, 16, 70, 16, 100.0, 1.0),    # a prime number of heads: one block of thirteen warps
+    (64, 32, 8, 32, 32, 64, 16, 100.0, 2.0),     # bfloat16 prompts: two blocks of sixteen heads share a tile
+    (48, 20, 4, 48, 48, 90, 24, 1000.0, 1.0),    # two blocks of ten heads, five heads a kv head
 ]
 
 
